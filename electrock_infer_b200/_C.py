@@ -1,0 +1,164 @@
+"""Drop-in for the reference's native module ``electrock_infer._C`` (pytorch_bind.cpp:11-50).
+
+The five MoE ops keep the reference's names, keyword names, in-place output convention
+(everything is caller-allocated, every op returns ``None``) and error type (``RuntimeError``,
+what a failed ``TORCH_CHECK`` surfaces as).  Each forwards raw device pointers to the C-ABI
+library on the current CUDA stream of the tensor's device; nothing is computed in Python.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_FLOAT_TAGS = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+_INT_TAGS = {torch.int32: _lib.I32, torch.int64: _lib.I64, torch.int16: _lib.I16,
+             torch.int8: _lib.I8, torch.uint8: _lib.U8}
+
+
+def _require_cuda(name: str, *tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError(f"{name}: tensors must be on a CUDA device (got {t.device}); "
+                               "there is no CPU implementation")
+        if t.device != dev:
+            raise RuntimeError(f"{name}: tensors are on different devices ({dev} vs {t.device})")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name}: tensors must be contiguous")
+    return dev
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _float_tag(name: str, t: torch.Tensor) -> int:
+    try:
+        return _FLOAT_TAGS[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"{name}: unsupported dtype {t.dtype}") from None
+
+
+def topk_softmax(topk_weights: torch.Tensor, topk_indices: torch.Tensor,
+                 gating_output: torch.Tensor, renormalize: bool = False) -> None:
+    """softmax over 8 experts + top-2 (src/topk_softmax_kernels.cu:85-111).
+
+    ``topk_weights`` f32 ``[T, 2]`` and ``topk_indices`` i32 ``[T, 2]`` are overwritten.  Like the
+    reference the probabilities are not renormalised unless ``renormalize`` (an extension) is set.
+    Unlike the reference, bf16/fp16 logits are accepted directly (no ``.float()`` copy needed).
+    """
+    name = "topk_softmax"
+    dev = _require_cuda(name, topk_weights, topk_indices, gating_output)
+    if topk_weights.dtype != torch.float32 or topk_indices.dtype != torch.int32:
+        raise RuntimeError(f"{name}: topk_weights must be float32 and topk_indices int32")
+    num_experts = gating_output.size(-1)
+    num_tokens = gating_output.numel() // max(num_experts, 1)
+    topk = topk_weights.size(-1)
+    if topk_weights.numel() != num_tokens * topk or topk_indices.numel() != num_tokens * topk:
+        raise RuntimeError(f"{name}: outputs must hold num_tokens * topk elements")
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200moe_topk_softmax(
+            topk_weights.data_ptr(), topk_indices.data_ptr(), gating_output.data_ptr(),
+            _float_tag(name, gating_output), num_tokens, num_experts, topk, int(renormalize),
+            _stream(dev))
+    _lib.check(rc, name)
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: int,
+                         sorted_token_ids: torch.Tensor, expert_ids: torch.Tensor,
+                         num_tokens_post_pad: torch.Tensor,
+                         expert_offsets: torch.Tensor | None = None,
+                         fill_pads: bool = False) -> None:
+    """Stable counting sort of pair indices by expert with per-expert padding
+    (src/moe_align_block_size.cu:140-230).
+
+    With the defaults the op writes exactly what the reference kernel writes (padding slots and
+    the tail are left as the caller prefilled them).  ``fill_pads=True`` makes the kernel write the
+    ``-1`` padding itself; ``expert_offsets`` (i32 ``[num_experts + 1]``) optionally receives the
+    padded start offset of every expert.  Both are extensions.
+    """
+    name = "moe_align_block_size"
+    outs = [sorted_token_ids, expert_ids, num_tokens_post_pad]
+    if expert_offsets is not None:
+        outs.append(expert_offsets)
+    dev = _require_cuda(name, topk_ids, *outs)
+    for t in outs:
+        if t.dtype != torch.int32:
+            raise RuntimeError(f"{name}: outputs must be int32")
+    if topk_ids.dtype not in _INT_TAGS:
+        raise RuntimeError(f"{name}: topk_ids must be an integral tensor, got {topk_ids.dtype}")
+    if expert_offsets is not None and expert_offsets.numel() < num_experts + 1:
+        raise RuntimeError(f"{name}: expert_offsets needs num_experts + 1 elements")
+    if num_tokens_post_pad.numel() < 1:
+        raise RuntimeError(f"{name}: num_tokens_post_pad needs one element")
+    lib = _lib.load()
+    numel = topk_ids.numel()
+    ws_bytes = lib.b200moe_align_workspace_bytes(numel, num_experts)
+    ws = None
+    if ws_bytes:
+        ws = torch.empty(ws_bytes // 4, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.b200moe_align_block_size(
+            topk_ids.data_ptr(), _INT_TAGS[topk_ids.dtype], numel, int(num_experts),
+            int(block_size), sorted_token_ids.data_ptr(), sorted_token_ids.numel(),
+            expert_ids.data_ptr(), expert_ids.numel(), num_tokens_post_pad.data_ptr(),
+            expert_offsets.data_ptr() if expert_offsets is not None else None, int(fill_pads),
+            ws.data_ptr() if ws is not None else None, ws_bytes, _stream(dev))
+    _lib.check(rc, name)
+    if ws is not None:
+        ws.record_stream(torch.cuda.current_stream(dev))
+
+
+def silu_and_mul(out: torch.Tensor, input: torch.Tensor) -> None:  # noqa: A002 - reference name
+    """``out[..., j] = silu(input[..., j]) * input[..., d + j]``
+    (src/activation_kernels.cu:97-150)."""
+    name = "silu_and_mul"
+    dev = _require_cuda(name, out, input)
+    if input.dim() < 2:
+        raise RuntimeError(f"{name}: Input must have at least 2 dimensions!")
+    d = input.size(-1) // 2
+    if input.size(-1) != 2 * d:
+        raise RuntimeError(f"{name}: Input last dimension must be 2*d!")
+    if out.size(-1) != d:
+        raise RuntimeError(f"{name}: Output last dimension must be d!")
+    if out.dtype != input.dtype:
+        raise RuntimeError(f"{name}: out and input must have the same dtype")
+    rows = input.numel() // (2 * d) if d else 0
+    if out.numel() != rows * d:
+        raise RuntimeError(f"{name}: out holds {out.numel()} elements, expected {rows * d}")
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200moe_silu_and_mul(out.data_ptr(), input.data_ptr(),
+                                              _float_tag(name, input), rows, d, _stream(dev))
+    _lib.check(rc, name)
+
+
+def _moe_sum(name: str, input: torch.Tensor, output: torch.Tensor, layout: int) -> None:  # noqa: A002
+    dev = _require_cuda(name, input, output)
+    if input.dim() != 3:
+        raise RuntimeError(f"{name}: input must be 3-dimensional")
+    if input.dtype != output.dtype:
+        raise RuntimeError(f"{name}: input and output must have the same dtype")
+    if layout == 0:
+        topk, hidden = input.size(1), input.size(2)
+    else:
+        hidden, topk = input.size(1), input.size(2)
+    num_tokens = output.numel() // hidden if hidden else 0
+    if input.numel() != num_tokens * topk * hidden:
+        raise RuntimeError(f"{name}: input and output shapes do not match")
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200moe_moe_sum(input.data_ptr(), output.data_ptr(),
+                                         _float_tag(name, input), num_tokens, hidden, topk,
+                                         layout, _stream(dev))
+    _lib.check(rc, name)
+
+
+def moe_sum(input: torch.Tensor, output: torch.Tensor) -> None:  # noqa: A002
+    """``output[t] = input[t, 0] + input[t, 1]`` for ``input [T, 2, H]`` (src/moe_sum.cu:50-74)."""
+    _moe_sum("moe_sum", input, output, 0)
+
+
+def moe_sum_efficient(input: torch.Tensor, output: torch.Tensor) -> None:  # noqa: A002
+    """Same sum for the interleaved layout ``input [T, H, 2]``
+    (src/moe_sum_efficient.cu:52-79); bf16 is accepted in addition to fp32/fp16."""
+    _moe_sum("moe_sum_efficient", input, output, 1)

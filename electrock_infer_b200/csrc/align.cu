@@ -1,0 +1,405 @@
+// Token alignment (moe_align_block_size): a stable counting sort of the flat (token, slot) pair
+// indices by expert, each expert's run padded to a multiple of block_size.
+//
+// Output contract follows src/moe_align_block_size.cu:58-133 of the reference:
+//   cumsum[e+1] = cumsum[e] + ceil(cnt[e] / bs) * bs;  *num_tokens_post_pad = cumsum[E];
+//   expert_ids[b] = e for the blocks of e;  sorted[cumsum[e] + r] = the r-th smallest pair index
+//   routed to e.
+//
+// The reference runs one CTA of one warp.  Here a warp ranks 128 consecutive ids per step: every
+// lane loads four ids with one 16-byte load, keeps eight per-expert counters packed as bytes of a
+// 64-bit word, and one packed warp prefix scan yields the stable rank of all 128 ids at once.
+// Inputs up to kSinglePassMax ids run as one CTA in one launch (the layer's case: a few thousand
+// to a few tens of thousands of ids).  Longer inputs use three launches over segments of
+// kSegment ids: per-segment histogram, a one-CTA scan over segments, and a scatter that re-reads
+// the ids (from L2 at these sizes).
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kMaxExperts = 8;          // counters are the 8 bytes of a 64-bit word
+constexpr int kIdsPerLane = 4;
+constexpr int kIdsPerWarpStep = 32 * kIdsPerLane;  // 128: a per-expert count fits in a byte
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+constexpr int64_t kSinglePassMax = 65536;
+
+constexpr int kSegThreads = 256;
+constexpr int kSegWarps = kSegThreads / 32;
+constexpr int kSegment = 8192;  // ids per CTA of the multi-launch path
+
+template <typename T>
+__device__ __forceinline__ void load_ids4(const T* __restrict__ ids, int64_t base, int64_t numel,
+                                          int num_experts, int (&e)[4]) {
+  // Expert index of ids[base .. base+3]; -1 for positions past the end or out-of-range experts.
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int x = -1;
+    if (base + j < numel) {
+      const long long raw = static_cast<long long>(ids[base + j]);
+      x = (raw >= 0 && raw < num_experts) ? static_cast<int>(raw) : -1;
+    }
+    e[j] = x;
+  }
+}
+
+template <>
+__device__ __forceinline__ void load_ids4<int32_t>(const int32_t* __restrict__ ids, int64_t base,
+                                                   int64_t numel, int num_experts, int (&e)[4]) {
+  if (base + 3 < numel) {
+    const int4 x = __ldg(reinterpret_cast<const int4*>(ids + base));
+    e[0] = x.x; e[1] = x.y; e[2] = x.z; e[3] = x.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) e[j] = (base + j < numel) ? __ldg(ids + base + j) : -1;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (static_cast<unsigned>(e[j]) >= static_cast<unsigned>(num_experts)) e[j] = -1;
+}
+
+// Byte-packed histogram of four expert ids (-1 contributes nothing).
+__device__ __forceinline__ uint64_t pack_counts(const int (&e)[4]) {
+  uint64_t c = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (e[j] >= 0) c += 1ull << (8 * e[j]);
+  return c;
+}
+
+// Inclusive warp prefix sum of a byte-packed histogram (each byte stays <= 128).
+__device__ __forceinline__ uint64_t warp_inclusive_scan(uint64_t c, int lane) {
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint64_t o = __shfl_up_sync(0xffffffffu, c, d);
+    if (lane >= d) c += o;
+  }
+  return c;
+}
+
+__device__ __forceinline__ int byte_of(uint64_t c, int e) { return static_cast<int>((c >> (8 * e)) & 0xff); }
+
+// Counts the experts of ids[begin, end) handled by one warp; result replicated on all lanes.
+template <typename T>
+__device__ __forceinline__ void warp_count(const T* __restrict__ ids, int64_t begin, int64_t end,
+                                           int64_t numel, int num_experts, int lane,
+                                           int (&cnt)[kMaxExperts]) {
+#pragma unroll
+  for (int x = 0; x < kMaxExperts; ++x) cnt[x] = 0;
+  for (int64_t base = begin; base < end; base += kIdsPerWarpStep) {
+    int e[4];
+    load_ids4<T>(ids, base + lane * kIdsPerLane, end < numel ? end : numel, num_experts, e);
+    uint64_t c = pack_counts(e);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
+    // A byte can reach 128 only, so no carry crosses bytes.
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) cnt[x] += byte_of(c, x);
+  }
+}
+
+// Writes the stable positions of ids[begin, end) handled by one warp.  start[x] is the output
+// slot of the first id of expert x in this range and is advanced as the warp walks the range.
+template <typename T>
+__device__ __forceinline__ void warp_scatter(const T* __restrict__ ids, int64_t begin, int64_t end,
+                                             int64_t numel, int num_experts, int lane,
+                                             int (&start)[kMaxExperts],
+                                             int32_t* __restrict__ sorted) {
+  for (int64_t base = begin; base < end; base += kIdsPerWarpStep) {
+    int e[4];
+    const int64_t first = base + lane * kIdsPerLane;
+    load_ids4<T>(ids, first, end < numel ? end : numel, num_experts, e);
+    const uint64_t mine = pack_counts(e);
+    const uint64_t incl = warp_inclusive_scan(mine, lane);
+    uint64_t excl = incl - mine;
+    const uint64_t total = __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (e[j] >= 0) {
+        int s = 0;
+#pragma unroll
+        for (int x = 0; x < kMaxExperts; ++x)
+          if (x == e[j]) s = start[x];
+        sorted[s + byte_of(excl, e[j])] = static_cast<int32_t>(first + j);
+        excl += 1ull << (8 * e[j]);
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) start[x] += byte_of(total, x);
+  }
+}
+
+// Shared tail of both paths: given the total count per expert, thread 0 publishes the padded
+// offsets; then all threads write expert_ids and (optionally) the -1 padding.
+__device__ __forceinline__ void publish_offsets(const int* total, int num_experts, int block_size,
+                                                int* s_cumsum,
+                                                int32_t* __restrict__ num_tokens_post_pad,
+                                                int32_t* __restrict__ expert_offsets) {
+  int acc = 0;
+  s_cumsum[0] = 0;
+  for (int x = 0; x < num_experts; ++x) {
+    acc += (total[x] + block_size - 1) / block_size * block_size;
+    s_cumsum[x + 1] = acc;
+  }
+  *num_tokens_post_pad = acc;
+  if (expert_offsets)
+    for (int x = 0; x <= num_experts; ++x) expert_offsets[x] = s_cumsum[x];
+}
+
+__device__ __forceinline__ void write_blocks_and_pads(const int* s_cumsum, const int* total,
+                                                      int num_experts, int block_size,
+                                                      int32_t* __restrict__ sorted,
+                                                      int64_t sorted_capacity,
+                                                      int32_t* __restrict__ expert_ids,
+                                                      int fill_pads, int tid, int nthreads) {
+  const int npp = s_cumsum[num_experts];
+  const int nblocks = npp / block_size;
+  for (int b = tid; b < nblocks; b += nthreads) {
+    const int slot = b * block_size;
+    int x = 0;
+    while (x + 1 < num_experts && slot >= s_cumsum[x + 1]) ++x;
+    expert_ids[b] = x;
+  }
+  if (fill_pads) {
+    for (int x = 0; x < num_experts; ++x) {
+      const int lo = s_cumsum[x] + total[x], hi = s_cumsum[x + 1];
+      for (int i = lo + tid; i < hi; i += nthreads) sorted[i] = -1;
+    }
+    for (int64_t i = npp + tid; i < sorted_capacity; i += nthreads) sorted[i] = -1;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One launch, one CTA: count, scan and scatter with every warp owning a contiguous range.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+align_single_cta_kernel(const T* __restrict__ ids, int64_t numel, int num_experts, int block_size,
+                        int32_t* __restrict__ sorted, int64_t sorted_capacity,
+                        int32_t* __restrict__ expert_ids,
+                        int32_t* __restrict__ num_tokens_post_pad,
+                        int32_t* __restrict__ expert_offsets, int fill_pads) {
+  __shared__ int s_warp_cnt[kWarps][kMaxExperts];
+  __shared__ int s_total[kMaxExperts];
+  __shared__ int s_cumsum[kMaxExperts + 1];
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // Contiguous range per warp, a multiple of the 128-id warp step.
+  const int64_t steps = ceil_div64(numel, kIdsPerWarpStep);
+  const int64_t per_warp = ceil_div64(steps, kWarps) * kIdsPerWarpStep;
+  const int64_t begin = min(static_cast<int64_t>(warp) * per_warp, numel);
+  const int64_t end = min(begin + per_warp, numel);
+
+  int cnt[kMaxExperts];
+  warp_count<T>(ids, begin, end, numel, num_experts, lane, cnt);
+  if (lane == 0) {
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) s_warp_cnt[warp][x] = cnt[x];
+  }
+  __syncthreads();
+
+  // Exclusive scan over warps, one thread per expert (32 serial adds).
+  if (threadIdx.x < kMaxExperts) {
+    int acc = 0;
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = s_warp_cnt[w][threadIdx.x];
+      s_warp_cnt[w][threadIdx.x] = acc;
+      acc += c;
+    }
+    s_total[threadIdx.x] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    publish_offsets(s_total, num_experts, block_size, s_cumsum, num_tokens_post_pad,
+                    expert_offsets);
+  __syncthreads();
+
+  write_blocks_and_pads(s_cumsum, s_total, num_experts, block_size, sorted, sorted_capacity,
+                        expert_ids, fill_pads, threadIdx.x, kThreads);
+
+  int start[kMaxExperts];
+#pragma unroll
+  for (int x = 0; x < kMaxExperts; ++x)
+    start[x] = (x < num_experts ? s_cumsum[x] : 0) + s_warp_cnt[warp][x];
+  warp_scatter<T>(ids, begin, end, numel, num_experts, lane, start, sorted);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Multi-launch path.  Workspace layout: int32 seg_counts[num_segments][kMaxExperts], rewritten in
+// place by the scan kernel into exclusive per-expert prefixes, followed by int32
+// meta[kMaxExperts + 1 + kMaxExperts] = padded offsets and totals.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kSegThreads)
+align_count_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
+                   int32_t* __restrict__ seg_counts) {
+  __shared__ int s_cnt[kSegWarps][kMaxExperts];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t seg_begin = static_cast<int64_t>(blockIdx.x) * kSegment;
+  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * (kSegment / kSegWarps), numel);
+  const int64_t end = min(begin + kSegment / kSegWarps, numel);
+  int cnt[kMaxExperts];
+  warp_count<T>(ids, begin, end, numel, num_experts, lane, cnt);
+  if (lane == 0) {
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) s_cnt[warp][x] = cnt[x];
+  }
+  __syncthreads();
+  if (threadIdx.x < kMaxExperts) {
+    int acc = 0;
+    for (int w = 0; w < kSegWarps; ++w) acc += s_cnt[w][threadIdx.x];
+    seg_counts[static_cast<int64_t>(blockIdx.x) * kMaxExperts + threadIdx.x] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+align_scan_kernel(int32_t* __restrict__ seg_counts, int64_t num_segments, int num_experts,
+                  int block_size, int32_t* __restrict__ meta, int32_t* __restrict__ sorted,
+                  int64_t sorted_capacity, int32_t* __restrict__ expert_ids,
+                  int32_t* __restrict__ num_tokens_post_pad, int32_t* __restrict__ expert_offsets,
+                  int fill_pads) {
+  // Warp x (x < num_experts) scans the counts of expert x over all segments.
+  __shared__ int s_total[kMaxExperts];
+  __shared__ int s_cumsum[kMaxExperts + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp < kMaxExperts) {
+    int carry = 0;
+    for (int64_t s0 = 0; s0 < num_segments; s0 += 32) {
+      const int64_t s = s0 + lane;
+      const int c = (s < num_segments) ? seg_counts[s * kMaxExperts + warp] : 0;
+      int incl = c;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      if (s < num_segments) seg_counts[s * kMaxExperts + warp] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_total[warp] = carry;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    publish_offsets(s_total, num_experts, block_size, s_cumsum, num_tokens_post_pad,
+                    expert_offsets);
+    for (int x = 0; x <= kMaxExperts; ++x) meta[x] = s_cumsum[x <= num_experts ? x : num_experts];
+  }
+  __syncthreads();
+  write_blocks_and_pads(s_cumsum, s_total, num_experts, block_size, sorted, sorted_capacity,
+                        expert_ids, fill_pads, threadIdx.x, kThreads);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSegThreads)
+align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
+                     const int32_t* __restrict__ seg_prefix, const int32_t* __restrict__ meta,
+                     int32_t* __restrict__ sorted) {
+  __shared__ int s_cnt[kSegWarps][kMaxExperts];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t seg_begin = static_cast<int64_t>(blockIdx.x) * kSegment;
+  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * (kSegment / kSegWarps), numel);
+  const int64_t end = min(begin + kSegment / kSegWarps, numel);
+  int cnt[kMaxExperts];
+  warp_count<T>(ids, begin, end, numel, num_experts, lane, cnt);
+  if (lane == 0) {
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) s_cnt[warp][x] = cnt[x];
+  }
+  __syncthreads();
+  int start[kMaxExperts];
+#pragma unroll
+  for (int x = 0; x < kMaxExperts; ++x) {
+    int acc = meta[x] + seg_prefix[static_cast<int64_t>(blockIdx.x) * kMaxExperts + x];
+    for (int w = 0; w < warp; ++w) acc += s_cnt[w][x];
+    start[x] = acc;
+  }
+  warp_scatter<T>(ids, begin, end, numel, num_experts, lane, start, sorted);
+}
+
+template <typename T>
+int run(const void* ids_v, int64_t numel, int E, int bs, int32_t* sorted, int64_t cap,
+        int32_t* expert_ids, int32_t* npp, int32_t* offsets, int fill, void* ws, size_t ws_bytes,
+        cudaStream_t st) {
+  const T* ids = static_cast<const T*>(ids_v);
+  if (numel <= kSinglePassMax) {
+    align_single_cta_kernel<T><<<1, kThreads, 0, st>>>(ids, numel, E, bs, sorted, cap, expert_ids,
+                                                       npp, offsets, fill);
+    return check_launch("moe_align_block_size");
+  }
+  const size_t need = b200moe_align_workspace_bytes(numel, E);
+  if (!ws || ws_bytes < need)
+    return fail(B200MOE_ERR_WORKSPACE,
+                "moe_align_block_size: %lld ids need a workspace of %zu bytes, got %zu",
+                (long long)numel, need, ws ? ws_bytes : (size_t)0);
+  if (!aligned_to(ws, 4)) return fail(B200MOE_ERR_ALIGN, "moe_align_block_size: workspace alignment");
+  const int64_t nseg = ceil_div64(numel, kSegment);
+  int32_t* seg = static_cast<int32_t*>(ws);
+  int32_t* meta = seg + nseg * kMaxExperts;
+  align_count_kernel<T><<<static_cast<unsigned>(nseg), kSegThreads, 0, st>>>(ids, numel, E, seg);
+  align_scan_kernel<<<1, kThreads, 0, st>>>(seg, nseg, E, bs, meta, sorted, cap, expert_ids, npp,
+                                            offsets, fill);
+  align_scatter_kernel<T><<<static_cast<unsigned>(nseg), kSegThreads, 0, st>>>(ids, numel, E, seg,
+                                                                               meta, sorted);
+  return check_launch("moe_align_block_size");
+}
+
+}  // namespace
+}  // namespace b200moe
+
+extern "C" size_t b200moe_align_workspace_bytes(int64_t numel, int num_experts) {
+  using namespace b200moe;
+  (void)num_experts;
+  if (numel <= kSinglePassMax) return 0;
+  const int64_t nseg = ceil_div64(numel, kSegment);
+  return static_cast<size_t>(nseg * kMaxExperts + 2 * kMaxExperts + 1) * sizeof(int32_t);
+}
+
+extern "C" int64_t b200moe_align_single_pass_max(void) { return b200moe::kSinglePassMax; }
+extern "C" int b200moe_align_max_experts(void) { return b200moe::kMaxExperts; }
+
+extern "C" int b200moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel,
+                                        int num_experts, int block_size, int32_t* sorted_token_ids,
+                                        int64_t sorted_capacity, int32_t* expert_ids,
+                                        int64_t expert_ids_capacity, int32_t* num_tokens_post_pad,
+                                        int32_t* expert_offsets, int fill_pads, void* workspace,
+                                        size_t workspace_bytes, b200moe_stream_t stream) {
+  using namespace b200moe;
+  if (num_experts < 1 || num_experts > kMaxExperts)
+    return fail(B200MOE_ERR_SHAPE, "moe_align_block_size: num_experts=%d, supported 1..%d",
+                num_experts, kMaxExperts);
+  if (block_size < 1) return fail(B200MOE_ERR_SHAPE, "moe_align_block_size: block_size=%d", block_size);
+  if (numel < 0 || numel > 0x7fffffffLL - (int64_t)num_experts * block_size)
+    return fail(B200MOE_ERR_SHAPE, "moe_align_block_size: numel=%lld out of range", (long long)numel);
+  const int64_t need_sorted = numel + static_cast<int64_t>(num_experts) * (block_size - 1);
+  if (sorted_capacity < need_sorted)
+    return fail(B200MOE_ERR_SHAPE,
+                "moe_align_block_size: sorted_token_ids holds %lld, needs numel + E*(block-1) = %lld",
+                (long long)sorted_capacity, (long long)need_sorted);
+  if (expert_ids_capacity < ceil_div64(need_sorted, block_size))
+    return fail(B200MOE_ERR_SHAPE, "moe_align_block_size: expert_ids holds %lld, needs %lld",
+                (long long)expert_ids_capacity, (long long)ceil_div64(need_sorted, block_size));
+  if (!sorted_token_ids || !expert_ids || !num_tokens_post_pad || (numel > 0 && !topk_ids))
+    return fail(B200MOE_ERR_NULL, "moe_align_block_size: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define B200MOE_ALIGN_CASE(tag, type)                                                            \
+  case tag:                                                                                      \
+    return run<type>(topk_ids, numel, num_experts, block_size, sorted_token_ids, sorted_capacity, \
+                     expert_ids, num_tokens_post_pad, expert_offsets, fill_pads, workspace,      \
+                     workspace_bytes, st)
+  switch (ids_dtype) {
+    case B200MOE_I32:
+      if (!aligned_to(topk_ids, 16))
+        return fail(B200MOE_ERR_ALIGN, "moe_align_block_size: int32 topk_ids must be 16-byte aligned");
+      return run<int32_t>(topk_ids, numel, num_experts, block_size, sorted_token_ids,
+                          sorted_capacity, expert_ids, num_tokens_post_pad, expert_offsets,
+                          fill_pads, workspace, workspace_bytes, st);
+    B200MOE_ALIGN_CASE(B200MOE_I64, int64_t);
+    B200MOE_ALIGN_CASE(B200MOE_I16, int16_t);
+    B200MOE_ALIGN_CASE(B200MOE_I8, int8_t);
+    B200MOE_ALIGN_CASE(B200MOE_U8, uint8_t);
+    default:
+      return fail(B200MOE_ERR_DTYPE, "moe_align_block_size: unsupported ids dtype %d", ids_dtype);
+  }
+#undef B200MOE_ALIGN_CASE
+}

@@ -1,0 +1,61 @@
+// Row gather into expert-sorted order: dst[s, :] = src[sorted_token_ids[s] / top_k, :].
+//
+// The reference's grouped GEMM gathers its A rows with per-element pointer arithmetic inside the
+// K loop (layers/moe/fused_moe.py:88-91).  Here the rows are copied once, with 16-byte accesses,
+// so that the tensor-core kernels read dense TMA tiles.  Padding slots are zero-filled; slots at
+// or beyond *num_tokens_post_pad are not touched.
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kRowsPerCta = 4;  // one 64-thread group per row; each thread moves 16 B per step
+
+__global__ void __launch_bounds__(kThreads)
+gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                   const int32_t* __restrict__ sorted, const int32_t* __restrict__ npp_ptr,
+                   int64_t capacity, int64_t num_src_rows, int row_vecs, int top_k) {
+  const int64_t npp = min(static_cast<int64_t>(*npp_ptr), capacity);
+  const int group = threadIdx.x / (kThreads / kRowsPerCta);
+  const int t = threadIdx.x % (kThreads / kRowsPerCta);
+  for (int64_t s = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + group; s < npp;
+       s += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
+    const int id = sorted[s];
+    const int64_t row = id >= 0 ? id / top_k : -1;
+    uint4* d = dst + s * row_vecs;
+    if (row >= 0 && row < num_src_rows) {
+      const uint4* p = src + row * row_vecs;
+      for (int c = t; c < row_vecs; c += kThreads / kRowsPerCta) d[c] = __ldg(p + c);
+    } else {
+      for (int c = t; c < row_vecs; c += kThreads / kRowsPerCta) d[c] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_gather_rows(const void* src, void* dst, const int32_t* sorted_token_ids,
+                                   const int32_t* num_tokens_post_pad, int64_t sorted_capacity,
+                                   int64_t num_src_rows, int64_t row_elems, int top_k,
+                                   b200moe_stream_t stream) {
+  using namespace b200moe;
+  if (row_elems <= 0 || row_elems % 8 != 0)
+    return fail(B200MOE_ERR_SHAPE, "gather_rows: row_elems=%lld must be a positive multiple of 8",
+                (long long)row_elems);
+  if (top_k < 1) return fail(B200MOE_ERR_SHAPE, "gather_rows: top_k=%d", top_k);
+  if (sorted_capacity < 0 || num_src_rows < 0) return fail(B200MOE_ERR_SHAPE, "gather_rows: negative size");
+  if (sorted_capacity == 0) return B200MOE_OK;
+  if (!src || !dst || !sorted_token_ids || !num_tokens_post_pad)
+    return fail(B200MOE_ERR_NULL, "gather_rows: null pointer");
+  if (!aligned_to(src, 16) || !aligned_to(dst, 16))
+    return fail(B200MOE_ERR_ALIGN, "gather_rows: src and dst must be 16-byte aligned");
+  int64_t grid = ceil_div64(sorted_capacity, kRowsPerCta);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (grid > cap) grid = cap;
+  gather_rows_kernel<<<static_cast<unsigned>(grid), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), sorted_token_ids,
+      num_tokens_post_pad, sorted_capacity, num_src_rows, static_cast<int>(row_elems / 8), top_k);
+  return check_launch("gather_rows");
+}

@@ -1,0 +1,588 @@
+// Grouped expert GEMMs of the Mixtral MoE layer for sm_100a: tcgen05.mma with fp32 accumulators in
+// tensor memory (TMEM), operands staged in shared memory by TMA, persistent warp-specialised CTAs.
+//
+//   mode kW13: act[s, j]  = bf16( silu(g) * u ),  g/u = rows j and inter + j of w13[e]
+//   mode kW2 : out[p, n]  = bf16( topk_weights[p] * sum_k act[s, k] * w2[e, n, k] ),  p = sorted[s]
+//
+// Both replace the reference's Triton kernel (layers/moe/fused_moe.py:15-125) for its two call
+// sites (:250-255 and :282-287); the first also absorbs _C.silu_and_mul (:272).
+//
+// Work decomposition.  Rows are in expert-sorted, block-padded order (the output of token
+// alignment with block 128), so every 128-row M block belongs to one expert.  A tile is
+// 128 rows x 256 accumulator columns; for w13 the 256 columns are 128 gate columns followed by
+// the 128 matching up columns, fetched as two TMA boxes of the unmodified [E, 2*inter, hidden]
+// parameter, so that SiLU(g)*u is formed inside one thread without any exchange.  Tiles are
+// numbered expert-major, then N tile, then M block (M fastest): CTAs running side by side share
+// a weight tile through L2 while the expert's activation rows stay L2-resident.
+//
+// CTA layout (192 threads, one CTA per SM, grid = number of SMs):
+//   warp 0      TMA producer (one lane)         smem ring of kStages x (A 16 KiB + B 32 KiB)
+//   warp 1      tcgen05.mma issuer (one lane)   owns the TMEM allocation (512 columns = 2 tiles)
+//   warps 2..5  epilogue: tcgen05.ld -> math -> 16-byte global stores
+// Two TMEM accumulators let the epilogue of tile i overlap the MMAs of tile i+1.
+//
+// Every mbarrier wait is bounded (about a second of SM clocks).  A wait that runs out sets the
+// CTA's abort flag and a device status word, every role leaves its loop, TMEM is released and the
+// kernel returns; the host reads the word through b200moe_gemm_device_status().
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;           // accumulator columns per tile
+constexpr int kBlockK = 64;            // 64 bf16 = 128 bytes = one 128B-swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kABytes = kBlockM * kBlockK * 2;   // 16384
+constexpr int kBBytes = kBlockN * kBlockK * 2;   // 32768
+constexpr int kStageBytes = kABytes + kBBytes;   // 49152
+constexpr int kTmemCols = 512;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr int kMaxExperts = 64;
+constexpr long long kWaitCycles = 1ll << 31;
+
+constexpr int kSmemAlignSlack = 1024;
+constexpr int kSmemBytes = kStages * kStageBytes + kSmemAlignSlack;
+
+enum Mode { kW13 = 0, kW2 = 1 };
+
+// Device status word: 0 = fine; otherwise (role << 8) | barrier kind of the wait that ran out.
+__device__ int g_gemm_status = 0;
+
+// ------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait.  Returns false when the barrier did not flip in time or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int who) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        atomicCAS(&g_gemm_status, 0, who);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0),
+      "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane (base lane + i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes (64 elements)
+// stored with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the
+// leading byte offset is unused for this layout, descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  const uint32_t lo = (smem_addr & 0x3ffffu) >> 4;
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+// Instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                (static_cast<uint32_t>(kBlockN >> 3) << 17) |
+                                (static_cast<uint32_t>(kBlockM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+struct TileCoord {
+  int expert;
+  int m_block;
+  int n_tile;
+};
+
+// Tiles are numbered expert-major, then N tile, then M block within the expert.
+__device__ __forceinline__ TileCoord decode_tile(long long tile, int n_tiles, int num_experts,
+                                                 const int* blk_off) {
+  int e = 0;
+  while (e + 1 < num_experts && tile >= static_cast<long long>(blk_off[e + 1]) * n_tiles) ++e;
+  const int cnt = blk_off[e + 1] - blk_off[e];
+  const int local = static_cast<int>(tile - static_cast<long long>(blk_off[e]) * n_tiles);
+  TileCoord c;
+  c.expert = e;
+  c.n_tile = local / cnt;
+  c.m_block = blk_off[e] + local % cnt;
+  return c;
+}
+
+struct GemmParams {
+  const int32_t* expert_ids;
+  const int32_t* npp;            // *npp = padded row count (multiple of 128)
+  const int32_t* sorted;         // kW2: pair index of every slot (-1 = padding)
+  const float* topk_weights;     // kW2
+  __nv_bfloat16* out;            // kW13: act [capacity, inter]; kW2: out [num_pairs, hidden]
+  long long capacity;            // rows of the A operand
+  long long num_pairs;           // kW2
+  int num_experts;
+  int k_blocks;                  // K / 64
+  int n_tiles;                   // kW13: inter / 128; kW2: hidden / 256
+  int b_rows_per_expert;         // kW13: 2 * inter; kW2: hidden
+  int inter;                     // kW13: offset of the up rows inside an expert's w13
+  long long out_ld;              // leading dimension of out in elements
+};
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_blk_cnt[kMaxExperts];
+  __shared__ int s_blk_off[kMaxExperts + 1];
+  __shared__ int s_abort;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + kSmemAlignSlack - 1) &
+      ~static_cast<uintptr_t>(kSmemAlignSlack - 1));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ------------------------------------------------------------------ prologue
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], kEpilogueWarps);
+    }
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (threadIdx.x < kMaxExperts) s_blk_cnt[threadIdx.x] = 0;
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  __syncthreads();
+  long long npp = *p.npp;
+  if (npp > p.capacity) npp = p.capacity;
+  const int num_blocks = static_cast<int>(npp / kBlockM);
+  for (int b = threadIdx.x; b < num_blocks; b += kThreads) {
+    const int e = p.expert_ids[b];
+    if (e >= 0 && e < p.num_experts) atomicAdd(&s_blk_cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.num_experts; ++e) {
+      s_blk_off[e] = acc;
+      acc += s_blk_cnt[e];
+    }
+    s_blk_off[p.num_experts] = acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const long long total_tiles = static_cast<long long>(s_blk_off[p.num_experts]) * p.n_tiles;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
+        const int a_row = c.m_block * kBlockM;
+        const int b_row0 = c.expert * p.b_rows_per_expert +
+                           c.n_tile * (kMode == kW13 ? kBlockN / 2 : kBlockN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x101)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_expect_tx(&full_bar[stage], kStageBytes);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBlockK, a_row);
+          if (kMode == kW13) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
+            tma_load_2d(sb + kBBytes / 2, &tmap_b, &full_bar[stage], kb * kBlockK,
+                        b_row0 + p.inter);
+          } else {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long it = 0;
+      for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+        const int acc = static_cast<int>(it & 1);
+        const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, 0x201)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x202)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * kUmmaK * 2);
+            const uint64_t bdesc = make_smem_desc(sb + k * kUmmaK * 2);
+            umma_bf16(tmem_d, adesc, bdesc, kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage when these MMAs are done
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full_bar[acc]);  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;               // TMEM lanes this warp may read: 32*quarter ..
+    const int row_in_tile = quarter * 32 + lane;
+    bool ok = true;
+    long long it = 0;
+    for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+      const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
+      const int acc = static_cast<int>(it & 1);
+      const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+      const long long slot = static_cast<long long>(c.m_block) * kBlockM + row_in_tile;
+      // All lanes of the warp must leave together: the wait result is made warp-uniform.
+      int good = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, 0x301) ? 1 : 0;
+      good = __all_sync(0xffffffffu, good);
+      if (!good) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(acc * kBlockN);
+      if (kMode == kW13) {
+        __nv_bfloat16* dst = p.out + slot * p.out_ld + static_cast<long long>(c.n_tile) * (kBlockN / 2);
+#pragma unroll 1
+        for (int ch = 0; ch < (kBlockN / 2) / 32; ++ch) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + ch * 32, g);
+          tmem_ld_32x32(taddr + kBlockN / 2 + ch * 32, u);
+          tmem_ld_wait();
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+            const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            const float a0 = g0 / (1.0f + __expf(-g0)) * u0;
+            const float a1 = g1 / (1.0f + __expf(-g1)) * u1;
+            o[j] = pack_bf16(a0, a1);
+          }
+          uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            d4[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        }
+      } else {
+        const int pair = p.sorted[slot];
+        const bool live = pair >= 0 && pair < p.num_pairs;
+        const float w = live ? p.topk_weights[pair] : 0.f;
+        __nv_bfloat16* dst = p.out + static_cast<long long>(live ? pair : 0) * p.out_ld +
+                             static_cast<long long>(c.n_tile) * kBlockN;
+#pragma unroll 1
+        for (int ch = 0; ch < kBlockN / 32; ++ch) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + ch * 32, v);
+          tmem_ld_wait();
+          if (live) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[8 * q + 0]) * w, __uint_as_float(v[8 * q + 1]) * w);
+              o.y = pack_bf16(__uint_as_float(v[8 * q + 2]) * w, __uint_as_float(v[8 * q + 3]) * w);
+              o.z = pack_bf16(__uint_as_float(v[8 * q + 4]) * w, __uint_as_float(v[8 * q + 5]) * w);
+              o.w = pack_bf16(__uint_as_float(v[8 * q + 6]) * w, __uint_as_float(v[8 * q + 7]) * w);
+              d4[q] = o;
+            }
+          }
+        }
+      }
+      // Hand the accumulator back to the MMA warp.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // Give bulk copies that may still be in flight time to land before shared memory is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < (1ll << 22)) {}
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------ host side
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault,
+                                         &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] (cols contiguous), box = box_rows x 64 columns, 128-byte swizzle.
+int make_tmap(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows,
+              const char* what) {
+  auto encode = get_encode_fn();
+  if (!encode) return fail(B200MOE_ERR_CUDA, "%s: cuTensorMapEncodeTiled is unavailable", what);
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200MOE_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
+  return B200MOE_OK;
+}
+
+template <int kMode>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+  // The attribute belongs to the function in the current context; setting it on every launch is
+  // cheap and keeps processes that drive several devices correct.
+  const cudaError_t attr_err = cudaFuncSetAttribute(
+      grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (attr_err != cudaSuccess)
+    return fail(B200MOE_ERR_CUDA, "grouped_gemm: cannot reserve %d bytes of shared memory: %s",
+                kSmemBytes, cudaGetErrorString(attr_err));
+  grouped_gemm_kernel<kMode><<<sm_count(), kThreads, kSmemBytes, st>>>(ta, tb, p);
+  return check_launch("grouped_gemm");
+}
+
+int check_common(const char* name, int num_experts, int64_t hidden, int64_t inter, int block_m,
+                 int64_t capacity) {
+  if (block_m != kBlockM)
+    return fail(B200MOE_ERR_SHAPE, "%s: block_m must be %d, got %d", name, kBlockM, block_m);
+  if (num_experts < 1 || num_experts > kMaxExperts)
+    return fail(B200MOE_ERR_SHAPE, "%s: num_experts=%d, supported 1..%d", name, num_experts, kMaxExperts);
+  if (hidden <= 0 || inter <= 0 || capacity < 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld inter=%lld capacity=%lld", name, (long long)hidden,
+                (long long)inter, (long long)capacity);
+  if (capacity > 0x7fffffffLL - kBlockM) return fail(B200MOE_ERR_SHAPE, "%s: capacity too large", name);
+  return B200MOE_OK;
+}
+
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void* w13, void* act,
+                                               const int32_t* expert_ids,
+                                               const int32_t* num_tokens_post_pad,
+                                               int64_t sorted_capacity, int num_experts,
+                                               int64_t hidden, int64_t inter, int block_m,
+                                               b200moe_stream_t stream) {
+  using namespace b200moe;
+  const char* name = "grouped_gemm_w13_swiglu";
+  if (int rc = check_common(name, num_experts, hidden, inter, block_m, sorted_capacity)) return rc;
+  if (hidden % kBlockK != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld must be a multiple of %d", name, (long long)hidden, kBlockK);
+  if (inter % (kBlockN / 2) != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: intermediate size %lld must be a multiple of %d", name,
+                (long long)inter, kBlockN / 2);
+  if (sorted_capacity < kBlockM) return B200MOE_OK;  // no complete block can exist
+  if (!a_sorted || !w13 || !act || !expert_ids || !num_tokens_post_pad)
+    return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
+  if (!aligned_to(a_sorted, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16))
+    return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap(&ta, a_sorted, sorted_capacity, hidden, kBlockM, name)) return rc;
+  if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden,
+                         kBlockN / 2, name))
+    return rc;
+  GemmParams p{};
+  p.expert_ids = expert_ids;
+  p.npp = num_tokens_post_pad;
+  p.out = static_cast<__nv_bfloat16*>(act);
+  p.capacity = sorted_capacity;
+  p.num_experts = num_experts;
+  p.k_blocks = static_cast<int>(hidden / kBlockK);
+  p.n_tiles = static_cast<int>(inter / (kBlockN / 2));
+  p.b_rows_per_expert = static_cast<int>(2 * inter);
+  p.inter = static_cast<int>(inter);
+  p.out_ld = inter;
+  return launch<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, void* out,
+                                             const float* topk_weights,
+                                             const int32_t* sorted_token_ids,
+                                             const int32_t* expert_ids,
+                                             const int32_t* num_tokens_post_pad,
+                                             int64_t sorted_capacity, int64_t num_pairs,
+                                             int num_experts, int64_t hidden, int64_t inter,
+                                             int block_m, b200moe_stream_t stream) {
+  using namespace b200moe;
+  const char* name = "grouped_gemm_w2_scale";
+  if (int rc = check_common(name, num_experts, hidden, inter, block_m, sorted_capacity)) return rc;
+  if (inter % kBlockK != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: intermediate size %lld must be a multiple of %d", name,
+                (long long)inter, kBlockK);
+  if (hidden % kBlockN != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld must be a multiple of %d", name, (long long)hidden, kBlockN);
+  if (num_pairs < 0) return fail(B200MOE_ERR_SHAPE, "%s: num_pairs=%lld", name, (long long)num_pairs);
+  if (sorted_capacity < kBlockM || num_pairs == 0) return B200MOE_OK;
+  if (!act || !w2 || !out || !topk_weights || !sorted_token_ids || !expert_ids || !num_tokens_post_pad)
+    return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
+  if (!aligned_to(act, 16) || !aligned_to(w2, 16) || !aligned_to(out, 16))
+    return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
+  if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter, kBlockN, name))
+    return rc;
+  GemmParams p{};
+  p.expert_ids = expert_ids;
+  p.npp = num_tokens_post_pad;
+  p.sorted = sorted_token_ids;
+  p.topk_weights = topk_weights;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.capacity = sorted_capacity;
+  p.num_pairs = num_pairs;
+  p.num_experts = num_experts;
+  p.k_blocks = static_cast<int>(inter / kBlockK);
+  p.n_tiles = static_cast<int>(hidden / kBlockN);
+  p.b_rows_per_expert = static_cast<int>(hidden);
+  p.inter = 0;
+  p.out_ld = hidden;
+  return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_gemm_device_status(int reset) {
+  using namespace b200moe;
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int));
+  if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "gemm_device_status: %s", cudaGetErrorString(e));
+  if (reset && v != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "gemm_device_status: %s", cudaGetErrorString(e));
+  }
+  return v;
+}

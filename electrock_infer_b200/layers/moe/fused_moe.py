@@ -1,0 +1,137 @@
+"""The MoE pipeline behind ``FusedMoE.forward``: router -> alignment -> grouped GEMM with SwiGLU
+-> grouped GEMM with routing weight -> combine.
+
+Function names, arguments and results follow the reference's layers/moe/fused_moe.py
+(``fused_topk`` :130-164, ``fused_experts`` :170-293).  The reference runs about five torch
+kernels for routing, four launches for alignment, two Triton GEMMs, ``silu_and_mul`` and
+``moe_sum``; here one call is six launches of the C-ABI library:
+
+    topk_softmax (renormalising) -> align_block_size (writes its own padding) -> gather_rows
+    -> grouped_gemm_w13_swiglu -> grouped_gemm_w2_scale -> moe_sum
+"""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+from ... import _C, _lib
+
+# Rows per M tile of the tensor-core kernels; token alignment pads every expert to this.
+BLOCK_SIZE_M = 128
+
+
+def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: int,
+               renormalize: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """softmax(fp32) -> top-k -> optional renormalisation, in one kernel.
+
+    Returns ``(topk_weights f32 [T, topk], topk_ids i32 [T, topk])`` like the reference
+    (fused_moe.py:130-164).  On exactly equal logits the lower expert index is chosen, the rule of
+    the reference's own kernel (src/topk_softmax_kernels.cu:39,47).
+    """
+    assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
+    num_tokens = gating_output.shape[0]
+    topk_weights = torch.empty(num_tokens, topk, dtype=torch.float32, device=gating_output.device)
+    topk_ids = torch.empty(num_tokens, topk, dtype=torch.int32, device=gating_output.device)
+    _C.topk_softmax(topk_weights, topk_ids, gating_output.contiguous(), renormalize=renormalize)
+    return topk_weights, topk_ids
+
+
+class _Workspace:
+    """Scratch tensors of one ``fused_experts`` call, kept per (device, shape) so that steady-state
+    calls allocate nothing.  The reference allocates its three caches on every call
+    (fused_moe.py:223-239)."""
+
+    def __init__(self) -> None:
+        self._cache: Dict[tuple, dict] = {}
+
+    def get(self, device: torch.device, num_tokens: int, topk: int, num_experts: int,
+            hidden: int, inter: int) -> dict:
+        key = (device, num_tokens, topk, num_experts, hidden, inter)
+        ws = self._cache.get(key)
+        if ws is None:
+            if len(self._cache) >= 4:  # bounded: drop the oldest shape
+                self._cache.pop(next(iter(self._cache)))
+            pairs = num_tokens * topk
+            capacity = pairs + num_experts * (BLOCK_SIZE_M - 1)
+            blocks = (capacity + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M
+            i32 = dict(dtype=torch.int32, device=device)
+            bf16 = dict(dtype=torch.bfloat16, device=device)
+            ws = {
+                "capacity": capacity,
+                "topk_weights": torch.empty(num_tokens, topk, dtype=torch.float32, device=device),
+                "topk_ids": torch.empty(num_tokens, topk, **i32),
+                "sorted_ids": torch.empty(capacity, **i32),
+                "expert_ids": torch.zeros(blocks, **i32),
+                "num_post_pad": torch.zeros(1, **i32),
+                "a_sorted": torch.empty(capacity, hidden, **bf16),
+                "act": torch.empty(capacity, inter, **bf16),
+                "cache3": torch.empty(num_tokens, topk, hidden, **bf16),
+            }
+            self._cache[key] = ws
+        return ws
+
+
+_workspace = _Workspace()
+
+
+def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+                  gating_output: torch.Tensor, topk: int, renormalize: bool = True,
+                  inplace: bool = False, activation: str = "silu") -> torch.Tensor:
+    """Mixture-of-experts forward for ``hidden_states [T, H]`` (reference fused_moe.py:170-293).
+
+    ``w1`` is the stacked gate/up weight ``[E, 2*I, H]`` (gate rows first), ``w2`` is
+    ``[E, H, I]``, ``gating_output`` the router logits ``[T, E]`` in any float dtype.  With
+    ``inplace`` the result overwrites and aliases ``hidden_states``, as the layer relies on.
+    Tensors must be bf16 on a CUDA device: there is no other implementation behind this call.
+    """
+    if activation != "silu":
+        raise NotImplementedError(f"Activation {activation} not supported.")
+    if not hidden_states.is_cuda:
+        raise RuntimeError("fused_experts: tensors must be on a CUDA device; no CPU path exists")
+    if not (hidden_states.dtype == w1.dtype == w2.dtype == torch.bfloat16):
+        raise RuntimeError("fused_experts: hidden_states, w1 and w2 must be bfloat16 "
+                           f"(got {hidden_states.dtype}, {w1.dtype}, {w2.dtype})")
+    num_tokens, hidden = hidden_states.shape
+    num_experts, inter_x2, w1_k = w1.shape
+    inter = inter_x2 // 2
+    if w1_k != hidden or tuple(w2.shape) != (num_experts, hidden, inter):
+        raise RuntimeError(f"fused_experts: weight shapes {tuple(w1.shape)} / {tuple(w2.shape)} "
+                           f"do not match hidden={hidden}")
+    if gating_output.shape != (num_tokens, num_experts):
+        raise RuntimeError("fused_experts: gating_output must be [num_tokens, num_experts]")
+    for t in (hidden_states, w1, w2):
+        if not t.is_contiguous():
+            raise RuntimeError("fused_experts: hidden_states, w1 and w2 must be contiguous")
+
+    output = hidden_states if inplace else torch.empty_like(hidden_states)
+    if num_tokens == 0:
+        return output
+
+    dev = hidden_states.device
+    lib = _lib.load()
+    ws = _workspace.get(dev, num_tokens, topk, num_experts, hidden, inter)
+    capacity = ws["capacity"]
+    gating = gating_output if gating_output.is_contiguous() else gating_output.contiguous()
+
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _C.topk_softmax(ws["topk_weights"], ws["topk_ids"], gating, renormalize=renormalize)
+        _C.moe_align_block_size(ws["topk_ids"], num_experts, BLOCK_SIZE_M, ws["sorted_ids"],
+                                ws["expert_ids"], ws["num_post_pad"], fill_pads=True)
+        _lib.check(lib.b200moe_gather_rows(
+            hidden_states.data_ptr(), ws["a_sorted"].data_ptr(), ws["sorted_ids"].data_ptr(),
+            ws["num_post_pad"].data_ptr(), capacity, num_tokens, hidden, topk, stream),
+            "gather_rows")
+        _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
+            ws["a_sorted"].data_ptr(), w1.data_ptr(), ws["act"].data_ptr(),
+            ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity, num_experts,
+            hidden, inter, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
+        _lib.check(lib.b200moe_grouped_gemm_w2_scale(
+            ws["act"].data_ptr(), w2.data_ptr(), ws["cache3"].data_ptr(),
+            ws["topk_weights"].data_ptr(), ws["sorted_ids"].data_ptr(),
+            ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
+            num_tokens * topk, num_experts, hidden, inter, BLOCK_SIZE_M, stream),
+            "grouped_gemm_w2_scale")
+        _C.moe_sum(ws["cache3"], output)
+    return output

@@ -1,0 +1,86 @@
+"""``FusedMoE``: the tensor-parallel Mixtral expert layer with the reference's constructor,
+parameters, ``forward`` and ``weight_loader`` (layers/moe/mixtral_moe.py:8-152)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .fused_moe import fused_experts
+
+
+class FusedMoE(nn.Module):
+    """Unquantised Mixtral experts, sharded over the intermediate dimension.
+
+    Parameters (reference mixtral_moe.py:64-79):
+      ``w13_weight [E, 2 * I / tp, H]``  gate rows ``[0, I/tp)`` then up rows ``[I/tp, 2I/tp)``
+      ``w2_weight  [E, H, I / tp]``
+    both ``requires_grad=False`` and carrying ``.weight_loader``.
+
+    ``forward(hidden_states [T, H], router_logits [T, E])`` overwrites ``hidden_states`` with the
+    layer output and returns it (same storage); with ``reduce_results`` and ``tp_size > 1`` the
+    result is summed over the default process group first (:114-116).
+    """
+
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
+                 tp_size: Optional[int] = None, params_dtype: Optional[torch.dtype] = None,
+                 renormalize: bool = True, reduce_results: bool = False):
+        super().__init__()
+        initialised = dist.is_available() and dist.is_initialized()
+        if tp_size is None:
+            tp_size = dist.get_world_size() if initialised else 1
+        self.tp_size = tp_size
+        self.tp_rank = dist.get_rank() if initialised else 0
+
+        self.num_experts = num_experts
+        self.top_k = top_k
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.renormalize = renormalize
+        self.reduce_results = reduce_results
+        self.params_dtype = params_dtype or torch.get_default_dtype()
+
+        if self.intermediate_size % self.tp_size != 0:
+            raise ValueError(f"intermediate_size ({self.intermediate_size}) must be divisible by "
+                             f"tp_size ({self.tp_size})")
+        self.intermediate_size_per_partition = self.intermediate_size // self.tp_size
+
+        self.w13_weight = nn.Parameter(
+            torch.empty(self.num_experts, 2 * self.intermediate_size_per_partition,
+                        self.hidden_size, dtype=self.params_dtype), requires_grad=False)
+        self.w2_weight = nn.Parameter(
+            torch.empty(self.num_experts, self.hidden_size, self.intermediate_size_per_partition,
+                        dtype=self.params_dtype), requires_grad=False)
+        self.w13_weight.weight_loader = self.weight_loader
+        self.w2_weight.weight_loader = self.weight_loader
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        final_hidden_states = fused_experts(
+            hidden_states=hidden_states, w1=self.w13_weight, w2=self.w2_weight,
+            gating_output=router_logits, topk=self.top_k, renormalize=self.renormalize,
+            inplace=True, activation="silu")
+        if self.reduce_results and self.tp_size > 1:
+            dist.all_reduce(final_hidden_states)
+        return final_hidden_states
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, shard_id: str,
+                      expert_id: int) -> None:
+        """Copies this rank's slice of one checkpoint tensor into the stacked parameter
+        (reference mixtral_moe.py:121-152): ``w1``/``w3`` are ``[I, H]`` and are sliced by rows
+        into the gate/up halves of ``w13_weight[expert_id]``; ``w2`` is ``[H, I]`` and is sliced
+        by columns."""
+        shard = self.intermediate_size_per_partition
+        param_data = param.data[expert_id]
+        if shard_id in ("w1", "w3"):
+            loaded = loaded_weight.narrow(0, shard * self.tp_rank, shard)
+            if shard_id == "w1":
+                param_data[:shard, :].copy_(loaded)
+            else:
+                param_data[shard:, :].copy_(loaded)
+        elif shard_id == "w2":
+            loaded = loaded_weight.narrow(1, shard * self.tp_rank, shard)
+            param_data.copy_(loaded)
+        else:
+            raise ValueError(f"unknown shard_id: {shard_id}")

@@ -1,0 +1,198 @@
+/*
+ * b200moe.h — C ABI of libb200moe.so: the Mixtral mixture-of-experts layer hot path for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream, never synchronises, never allocates device memory and never
+ * throws.  The return value is 0 on success or a negative B200MOE_ERR_* code; the text of the
+ * most recent failure on the calling thread is available from b200moe_last_error().
+ *
+ * Each declaration names the reference interface it replaces (paths are relative to the
+ * electrock-infer source tree).
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ABI_VERSION 1
+
+/* Element types of floating-point tensors. */
+enum {
+  B200MOE_F32 = 0,
+  B200MOE_F16 = 1,
+  B200MOE_BF16 = 2
+};
+
+/* Element types of expert-index tensors (topk_ids). */
+enum {
+  B200MOE_I32 = 0,
+  B200MOE_I64 = 1,
+  B200MOE_I16 = 2,
+  B200MOE_I8 = 3,
+  B200MOE_U8 = 4
+};
+
+/* Status codes. */
+enum {
+  B200MOE_OK = 0,
+  B200MOE_ERR_SHAPE = -1,       /* a size the kernels do not support (the text says which) */
+  B200MOE_ERR_DTYPE = -2,       /* unsupported element type */
+  B200MOE_ERR_NULL = -3,        /* a required pointer is NULL */
+  B200MOE_ERR_WORKSPACE = -4,   /* workspace missing or too small */
+  B200MOE_ERR_ALIGN = -5,       /* a pointer is not aligned as required */
+  B200MOE_ERR_CUDA = -6,        /* a CUDA runtime / driver call failed */
+  B200MOE_ERR_UNSUPPORTED = -7  /* not built for this device */
+};
+
+/* A CUDA stream handle (cudaStream_t) passed as an opaque pointer; NULL is the default stream. */
+typedef void* b200moe_stream_t;
+
+/* ABI version of the loaded library (B200MOE_ABI_VERSION at build time). */
+int b200moe_abi_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* b200moe_last_error(void);
+
+/*
+ * Router: row-wise softmax over num_experts fp32/bf16/fp16 logits followed by top-2 selection.
+ * Replaces electrock_infer::topk_softmax (src/topk_softmax_kernels.cu:85-111, bound in
+ * pytorch_bind.cpp:24-29) and, with renormalize != 0, the torch router the layer really uses
+ * (layers/moe/softmax_topk.py:3-29 followed by layers/moe/fused_moe.py:161-162).
+ *
+ *   topk_weights  f32 [num_tokens, 2]   softmax probabilities of the two chosen experts, largest
+ *                                       first; divided by their sum when renormalize != 0
+ *   topk_indices  i32 [num_tokens, 2]   expert indices; on equal logits the lower index wins
+ *   gating_output [num_tokens, num_experts] logits of element type logits_dtype
+ *
+ * Like the reference, only num_experts == 8 and topk == 2 are accepted (B200MOE_ERR_SHAPE
+ * otherwise).  num_tokens may be 0 and need not be a multiple of anything.
+ */
+int b200moe_topk_softmax(float* topk_weights, int32_t* topk_indices, const void* gating_output,
+                         int logits_dtype, int64_t num_tokens, int num_experts, int topk,
+                         int renormalize, b200moe_stream_t stream);
+
+/*
+ * Token alignment: counting sort of the flat (token, slot) pairs by expert, each expert's run
+ * padded to a multiple of block_size.  Replaces electrock_infer::moe_align_block_size
+ * (src/moe_align_block_size.cu:140-230, bound in pytorch_bind.cpp:43-50).
+ *
+ *   topk_ids             [numel] expert index of pair i (row-major [num_tokens, topk])
+ *   sorted_token_ids     i32 [sorted_capacity], capacity >= numel + num_experts*(block_size-1);
+ *                        slot off[e] + r receives the r-th smallest pair index routed to e
+ *   expert_ids           i32 [expert_ids_capacity] expert of each block of block_size slots
+ *   num_tokens_post_pad  i32 [1] total padded length (sum over experts of the padded counts)
+ *   expert_offsets       optional i32 [num_experts + 1] padded start offset of every expert
+ *                        (no counterpart in the reference; may be NULL)
+ *
+ * With fill_pads == 0 padding slots and everything beyond num_tokens_post_pad are left untouched,
+ * exactly like the reference kernel, whose Python wrapper prefills -1
+ * (layers/moe/moe_align_block_size.py:39-42).  With fill_pads != 0 the kernel itself writes -1
+ * to every slot of sorted_token_ids that holds no pair, so no separate fill launch is needed.
+ *
+ * Inputs longer than b200moe_align_single_pass_max() need a workspace of
+ * b200moe_align_workspace_bytes() bytes (4-byte aligned device memory); shorter inputs run as
+ * one launch and ignore it.  num_experts must be between 1 and 8... see b200moe_align_max_experts().
+ * Pair indices with an expert outside [0, num_experts) are skipped.
+ */
+int b200moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel, int num_experts,
+                             int block_size, int32_t* sorted_token_ids, int64_t sorted_capacity,
+                             int32_t* expert_ids, int64_t expert_ids_capacity,
+                             int32_t* num_tokens_post_pad, int32_t* expert_offsets, int fill_pads,
+                             void* workspace, size_t workspace_bytes, b200moe_stream_t stream);
+size_t b200moe_align_workspace_bytes(int64_t numel, int num_experts);
+int64_t b200moe_align_single_pass_max(void);
+int b200moe_align_max_experts(void);
+
+/*
+ * SwiGLU activation as a stand-alone op: out[r, j] = cast(silu_f32(in[r, j])) * in[r, d + j].
+ * Replaces electrock_infer::silu_and_mul (src/activation_kernels.cu:97-150, bound in
+ * pytorch_bind.cpp:18-22): the 16-bit types round SiLU to the element type before the product
+ * and use the fast exponential; fp32 uses expf.
+ *
+ *   out [num_rows, d], input [num_rows, 2*d], both of element type dtype, contiguous.
+ */
+int b200moe_silu_and_mul(void* out, const void* input, int dtype, int64_t num_rows, int64_t d,
+                         b200moe_stream_t stream);
+
+/*
+ * Combine: out[t, :] = in[t, 0, :] + in[t, 1, :] in the element type.
+ * layout 0 replaces electrock_infer::moe_sum (input [num_tokens, 2, hidden],
+ * src/moe_sum.cu:50-74, pytorch_bind.cpp:31-35); layout 1 replaces
+ * electrock_infer::moe_sum_efficient (input [num_tokens, hidden, 2],
+ * src/moe_sum_efficient.cu:52-79, pytorch_bind.cpp:37-41; bf16 is accepted here too).
+ * topk must be 2, as in the reference.
+ */
+int b200moe_moe_sum(const void* input, void* output, int dtype, int64_t num_tokens, int64_t hidden,
+                    int topk, int layout, b200moe_stream_t stream);
+
+/*
+ * Row gather into expert-sorted order: dst[s, :] = src[sorted_token_ids[s] / top_k, :] for every
+ * slot s < *num_tokens_post_pad holding a pair; padding slots are zero-filled.  This is the
+ * A-operand addressing of the reference's grouped GEMM (layers/moe/fused_moe.py:88-91) done once
+ * ahead of the GEMM so that its tiles are dense.
+ *
+ *   src [num_src_rows, row_elems] bf16, dst [sorted_capacity, row_elems] bf16;
+ *   row_elems must be a multiple of 8.
+ */
+int b200moe_gather_rows(const void* src, void* dst, const int32_t* sorted_token_ids,
+                        const int32_t* num_tokens_post_pad, int64_t sorted_capacity,
+                        int64_t num_src_rows, int64_t row_elems, int top_k,
+                        b200moe_stream_t stream);
+
+/*
+ * Grouped expert GEMM 1 with the SwiGLU epilogue (tcgen05 / TMEM / TMA):
+ *   act[s, j] = bf16( silu(g) * u ),  g = sum_k a[s, k] * w13[e, j, k],
+ *                                     u = sum_k a[s, k] * w13[e, inter + j, k],
+ * for every slot s < *num_tokens_post_pad, e = expert_ids[s / block_m].  Accumulation, SiLU and
+ * the product are fp32; one rounding to bf16 at the end.  Replaces the first
+ * _invoke_fused_moe_kernel call plus _C.silu_and_mul (layers/moe/fused_moe.py:250-272,
+ * kernel :15-125).
+ *
+ *   a_sorted  bf16 [sorted_capacity, hidden]   rows in expert-sorted order (b200moe_gather_rows)
+ *   w13       bf16 [num_experts, 2*inter, hidden]   gate rows first, then up rows
+ *   act       bf16 [sorted_capacity, inter]
+ *   block_m   the block_size used for alignment; must be 128
+ *   hidden % 64 == 0, inter % 128 == 0 (inter % 64 == 0 when inter < 128 is not supported).
+ */
+int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void* w13, void* act,
+                                    const int32_t* expert_ids,
+                                    const int32_t* num_tokens_post_pad, int64_t sorted_capacity,
+                                    int num_experts, int64_t hidden, int64_t inter, int block_m,
+                                    b200moe_stream_t stream);
+
+/*
+ * Grouped expert GEMM 2 with the routing-weight epilogue:
+ *   out[p, n] = bf16( topk_weights[p] * sum_k act[s, k] * w2[e, n, k] ),  p = sorted_token_ids[s]
+ * for every slot s holding a pair; rows of out are indexed by the flat pair index p, i.e. out is
+ * the reference's [num_tokens, topk, hidden] cache.  Replaces the second
+ * _invoke_fused_moe_kernel call (layers/moe/fused_moe.py:282-287, epilogue :116-125).
+ *
+ *   act  bf16 [sorted_capacity, inter], w2 bf16 [num_experts, hidden, inter],
+ *   out  bf16 [num_pairs, hidden], topk_weights f32 [num_pairs];
+ *   hidden % 128 == 0 (output tile width), inter % 64 == 0, block_m == 128.
+ */
+int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, void* out,
+                                  const float* topk_weights, const int32_t* sorted_token_ids,
+                                  const int32_t* expert_ids, const int32_t* num_tokens_post_pad,
+                                  int64_t sorted_capacity, int64_t num_pairs, int num_experts,
+                                  int64_t hidden, int64_t inter, int block_m,
+                                  b200moe_stream_t stream);
+
+/*
+ * Device-side status word of the grouped GEMMs.  Their waits on memory barriers are bounded; a
+ * wait that runs out records a non-zero code here and the kernel returns.  Reading synchronises
+ * with the device.  Returns the code (0 = no error) or a negative B200MOE_ERR_*; `reset` != 0
+ * clears it.
+ */
+int b200moe_gemm_device_status(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

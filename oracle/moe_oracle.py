@@ -1,0 +1,238 @@
+"""CPU oracle of the Mixtral MoE hot path.  TEST INFRASTRUCTURE ONLY.
+
+Nothing in the product package imports this module: it exists so that tests, the smoke check and
+the CPU-baseline leg of the benchmark can compare the CUDA path with an independent restatement
+of the reference's algorithm.  Every function names the electrock-infer source it follows.
+
+Pinning: the functions here are checked against vectors produced by the reference's own Python
+code (``tests/golden/make_golden.py`` imports it from the reference tree and writes
+``tests/golden/*.npz``): the torch router, the pure-torch alignment golden of
+test/example/test_align_block.py, the HF-style block of test/example/verify_hf_moe.py and the
+reference ``fused_experts`` pipeline run through the Triton interpreter.  The reference's CUDA
+``topk_softmax`` kernel and ``moe_sum_efficient`` have no test of their own in the reference
+(parity for those two is pinned only against the torch formulas below).
+
+Integer work is numpy / plain C (``align_oracle.c``); floating-point work uses torch on the CPU
+because the reference's own CPU path is torch and its rounding rules for 16-bit types are the
+ones to reproduce.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from pathlib import Path
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_LIB = _HERE / "_build" / "liboracle.so"
+_clib = None
+
+
+def build_c_oracle(force: bool = False) -> Path:
+    """Compiles ``align_oracle.c`` with gcc (see the Makefile beside it)."""
+    src = _HERE / "align_oracle.c"
+    if force or not _LIB.exists() or _LIB.stat().st_mtime < src.stat().st_mtime:
+        _LIB.parent.mkdir(exist_ok=True)
+        subprocess.run(["gcc", "-O2", "-Wall", "-shared", "-fPIC", "-o", str(_LIB), str(src)],
+                       check=True)
+    return _LIB
+
+
+def _c() -> ctypes.CDLL:
+    global _clib
+    if _clib is None:
+        _clib = ctypes.CDLL(str(build_c_oracle()))
+        _clib.oracle_align_block_size.restype = ctypes.c_int
+        _clib.oracle_align_block_size.argtypes = [
+            ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+            ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+    return _clib
+
+
+# --------------------------------------------------------------------------------------- router
+def router_ref(logits: torch.Tensor, topk: int = 2,
+               renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """softmax in fp32 -> the ``topk`` largest, largest first -> optional renormalisation.
+
+    Follows layers/moe/softmax_topk.py:23-29 and layers/moe/fused_moe.py:161-162.  Ties are
+    broken towards the lower expert index, the rule of src/topk_softmax_kernels.cu:39,47
+    (``torch.topk`` leaves the order of equal values unspecified).  Returns
+    ``(weights f32 [T, topk], ids i32 [T, topk])``.
+    """
+    probs = torch.softmax(logits.detach().cpu().float(), dim=-1)
+    # Stable descending sort == lowest index first among equals.
+    order = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, :topk]
+    weights = torch.gather(probs, 1, order)
+    if renormalize:
+        weights = weights / weights.sum(dim=-1, keepdim=True)
+    return weights, order.to(torch.int32)
+
+
+def tie_rows(logits: torch.Tensor, topk: int = 2) -> torch.Tensor:
+    """Boolean mask of rows where the top-k *set or order* is decided by an exact tie, i.e. where
+    two implementations with different tie rules may legitimately disagree."""
+    vals = torch.sort(logits.detach().cpu().float(), dim=-1, descending=True).values
+    return (vals[:, : topk] == vals[:, 1: topk + 1]).any(dim=-1)
+
+
+# ------------------------------------------------------------------------------------ alignment
+def align_sizes(numel: int, block_size: int, num_experts: int) -> Tuple[int, int]:
+    """Buffer sizes of the reference wrapper (layers/moe/moe_align_block_size.py:32,41)."""
+    cap = numel + num_experts * (block_size - 1)
+    return cap, (cap + block_size - 1) // block_size
+
+
+def align_ref(topk_ids, block_size: int, num_experts: int, prefill: int = -1):
+    """Token alignment through the plain-C oracle, with the reference wrapper's allocation and
+    prefill rules (sorted ids prefilled with ``-1``, expert ids zero-filled;
+    layers/moe/moe_align_block_size.py:32-46).  Returns numpy arrays
+    ``(sorted_token_ids, expert_ids, num_tokens_post_pad, expert_offsets)``."""
+    ids = np.ascontiguousarray(np.asarray(topk_ids).reshape(-1).astype(np.int64))
+    cap, nblk = align_sizes(ids.size, block_size, num_experts)
+    sorted_ids = np.full(cap, prefill, dtype=np.int32)
+    expert_ids = np.zeros(nblk, dtype=np.int32)
+    npp = np.zeros(1, dtype=np.int32)
+    offsets = np.zeros(num_experts + 1, dtype=np.int32)
+    rc = _c().oracle_align_block_size(
+        ids.ctypes.data, ids.size, num_experts, block_size, sorted_ids.ctypes.data, cap,
+        expert_ids.ctypes.data, nblk, npp.ctypes.data, offsets.ctypes.data)
+    if rc != 0:
+        raise RuntimeError(f"oracle_align_block_size failed with {rc}")
+    return sorted_ids, expert_ids, npp, offsets
+
+
+def align_ref_numpy(topk_ids, block_size: int, num_experts: int, prefill: int = -1):
+    """The same contract written with numpy primitives (stable argsort), independent of the C
+    code; used to cross-check the two restatements against each other."""
+    ids = np.asarray(topk_ids).reshape(-1).astype(np.int64)
+    cap, nblk = align_sizes(ids.size, block_size, num_experts)
+    valid = (ids >= 0) & (ids < num_experts)
+    cnt = np.bincount(ids[valid], minlength=num_experts)
+    padded = (cnt + block_size - 1) // block_size * block_size
+    offsets = np.concatenate([[0], np.cumsum(padded)]).astype(np.int32)
+    sorted_ids = np.full(cap, prefill, dtype=np.int32)
+    expert_ids = np.zeros(nblk, dtype=np.int32)
+    idx = np.nonzero(valid)[0]
+    order = idx[np.argsort(ids[idx], kind="stable")]
+    start = 0
+    for e in range(num_experts):
+        sorted_ids[offsets[e]: offsets[e] + cnt[e]] = order[start: start + cnt[e]]
+        expert_ids[offsets[e] // block_size: offsets[e + 1] // block_size] = e
+        start += cnt[e]
+    return sorted_ids, expert_ids, np.array([offsets[-1]], dtype=np.int32), offsets
+
+
+# ---------------------------------------------------------------------------- activation / sum
+def silu_and_mul_ref(x: torch.Tensor) -> torch.Tensor:
+    """``out[..., j] = cast(silu_f32(x[..., j])) * x[..., d + j]`` with the product taken in the
+    element type (src/activation_kernels.cu:33-43; fp32: :74-92).  The CUDA kernels use the fast
+    exponential for 16-bit types, so agreement with this function is to within one unit in the
+    last place of the element type, not bit-exact."""
+    x = x.detach().cpu()
+    d = x.shape[-1] // 2
+    gate, up = x[..., :d], x[..., d:]
+    g32 = gate.float()
+    silu = (g32 / (1.0 + torch.exp(-g32))).to(x.dtype)
+    return silu * up  # torch multiplies 16-bit CPU tensors in fp32 and rounds once
+
+
+def moe_sum_ref(x: torch.Tensor) -> torch.Tensor:
+    """``[T, 2, H] -> [T, H]``: ``(0 + x[:, 0]) + x[:, 1]`` in the element type
+    (src/moe_sum.cu:35-41)."""
+    x = x.detach().cpu()
+    acc = torch.zeros_like(x[:, 0])
+    for k in range(x.shape[1]):
+        acc = acc + x[:, k]
+    return acc
+
+
+def moe_sum_efficient_ref(x: torch.Tensor) -> torch.Tensor:
+    """``[T, H, 2] -> [T, H]``: sum of the two adjacent values (src/moe_sum_efficient.cu:33-46)."""
+    x = x.detach().cpu()
+    return x[..., 0] + x[..., 1]
+
+
+# ------------------------------------------------------------------------------------ the layer
+def moe_block_ref(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, logits: torch.Tensor,
+                  topk: int = 2, renormalize: bool = True,
+                  compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Per-expert loop of the reference's torch golden (``MixtralSparseMoeBlock``,
+    test/example/verify_hf_moe.py:59-86): route, then for every expert gather its tokens, apply
+    ``w2(silu(w1 x) * w3 x)``, scale by the routing weight and ``index_add_`` into the output.
+
+    ``w13 [E, 2I, H]`` holds w1 (gate) rows first, then w3 (up) rows; ``w2 [E, H, I]``.
+    With ``compute_dtype=float32`` on bf16-valued inputs this is the fp32 reference the CUDA layer
+    is judged against; with ``bfloat16`` it reproduces the reference's CPU timing path.
+    """
+    x = x.detach().cpu()
+    weights, ids = router_ref(logits, topk, renormalize)
+    num_experts, inter_x2, _ = w13.shape
+    inter = inter_x2 // 2
+    xc = x.to(compute_dtype)
+    weights = weights.to(compute_dtype)
+    out = torch.zeros_like(xc)
+    ids64 = ids.long()
+    for e in range(num_experts):
+        tok, slot = torch.nonzero(ids64 == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        we = w13[e].detach().cpu().to(compute_dtype)
+        cur = xc[tok]
+        h = torch.nn.functional.silu(cur @ we[:inter].T) * (cur @ we[inter:].T)
+        y = h @ w2[e].detach().cpu().to(compute_dtype).T
+        out.index_add_(0, tok, y * weights[tok, slot].unsqueeze(1))
+    return out
+
+
+def _to_bf16(t: torch.Tensor, mode: str) -> torch.Tensor:
+    """fp32 -> bf16-valued fp32, rounding to nearest even (what a GPU cast does) or truncating
+    (what the Triton 3.6 CPU interpreter does for ``.to(tl.bfloat16)``)."""
+    t = t.float().contiguous()
+    if mode == "rne":
+        return t.to(torch.bfloat16).float()
+    if mode == "truncate":
+        return (t.view(torch.int32) & ~0xFFFF).view(torch.float32)
+    raise ValueError(mode)
+
+
+def fused_experts_ref(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, logits: torch.Tensor,
+                      topk: int = 2, renormalize: bool = True,
+                      bf16_cast: str = "rne") -> torch.Tensor:
+    """The reference pipeline with every rounding point it has (layers/moe/fused_moe.py:250-291):
+    GEMM1 fp32 accumulate -> bf16 (:120, compute_type is hard-coded bf16 at :254) -> stored in the
+    tensor dtype; SiLU in fp32 -> element type -> product in the element type; GEMM2 fp32
+    accumulate x fp32 routing weight -> bf16 (:116-120); sum of the two experts in the element
+    type.  Used to measure how far the reference's own result is from exact arithmetic.
+    ``bf16_cast="truncate"`` reproduces the reference run under the Triton CPU interpreter, whose
+    bf16 conversion drops the low mantissa bits instead of rounding."""
+    x = x.detach().cpu()
+    dt = x.dtype
+    weights, ids = router_ref(logits, topk, renormalize)
+    num_tokens = x.shape[0]
+    num_experts, inter_x2, _ = w13.shape
+    cache3 = torch.zeros(num_tokens, topk, x.shape[1], dtype=dt)
+    ids64 = ids.long()
+    for e in range(num_experts):
+        tok, slot = torch.nonzero(ids64 == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        c1 = _to_bf16(x[tok].float() @ w13[e].detach().cpu().float().T, bf16_cast).to(dt)
+        c2 = silu_and_mul_ref(c1)
+        y = c2.float() @ w2[e].detach().cpu().float().T
+        y = _to_bf16(y * weights[tok, slot].unsqueeze(1), bf16_cast).to(dt)
+        cache3[tok, slot] = y
+    return moe_sum_ref(cache3)
+
+
+def error_stats(got: torch.Tensor, want: torch.Tensor) -> dict:
+    """max-abs error, relative Frobenius error and the scale of ``want``."""
+    g, w = got.detach().cpu().double(), want.detach().cpu().double()
+    diff = (g - w).abs()
+    return {
+        "max_abs": float(diff.max()) if diff.numel() else 0.0,
+        "rel_fro": float(torch.linalg.norm(g - w) / max(float(torch.linalg.norm(w)), 1e-30)),
+        "ref_max_abs": float(w.abs().max()) if w.numel() else 0.0,
+    }
