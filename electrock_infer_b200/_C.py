@@ -63,6 +63,7 @@ def topk_softmax(topk_weights: torch.Tensor, topk_indices: torch.Tensor,
             _float_tag(name, gating_output), num_tokens, num_experts, topk, int(renormalize),
             _stream(dev))
     _lib.check(rc, name)
+    _lib.count_launches(1 if num_tokens else 0)
 
 
 def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: int,
@@ -106,6 +107,7 @@ def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: i
             expert_offsets.data_ptr() if expert_offsets is not None else None, int(fill_pads),
             ws.data_ptr() if ws is not None else None, ws_bytes, _stream(dev))
     _lib.check(rc, name)
+    _lib.count_launches(3 if ws is not None else 1)
     if ws is not None:
         ws.record_stream(torch.cuda.current_stream(dev))
 
@@ -131,6 +133,7 @@ def silu_and_mul(out: torch.Tensor, input: torch.Tensor) -> None:  # noqa: A002 
         rc = _lib.load().b200moe_silu_and_mul(out.data_ptr(), input.data_ptr(),
                                               _float_tag(name, input), rows, d, _stream(dev))
     _lib.check(rc, name)
+    _lib.count_launches(1 if rows * d else 0)
 
 
 def _moe_sum(name: str, input: torch.Tensor, output: torch.Tensor, layout: int) -> None:  # noqa: A002
@@ -151,6 +154,7 @@ def _moe_sum(name: str, input: torch.Tensor, output: torch.Tensor, layout: int) 
                                          _float_tag(name, input), num_tokens, hidden, topk,
                                          layout, _stream(dev))
     _lib.check(rc, name)
+    _lib.count_launches(1 if num_tokens * hidden else 0)
 
 
 def moe_sum(input: torch.Tensor, output: torch.Tensor) -> None:  # noqa: A002

@@ -42,6 +42,17 @@ SIGNATURES = {
 }
 
 _lib = None
+_launches = 0
+
+
+def count_launches(n: int = 1) -> None:
+    """Book-keeping for benchmarks: kernels launched through this binding so far."""
+    global _launches
+    _launches += n
+
+
+def launch_count() -> int:
+    return _launches
 
 
 def load() -> ctypes.CDLL:

@@ -74,6 +74,45 @@ class _Workspace:
 
 _workspace = _Workspace()
 
+# Optional per-kernel timing for benchmarks: when enabled, every launch of fused_experts is
+# bracketed by a pair of CUDA events on the launching stream.
+_timing_enabled = False
+_timing_events: list = []
+
+
+def enable_kernel_timing(on: bool) -> None:
+    global _timing_enabled
+    _timing_enabled = bool(on)
+    _timing_events.clear()
+
+
+def collect_kernel_timings() -> Dict[str, float]:
+    """Mean milliseconds per launch of every kernel timed since ``enable_kernel_timing(True)``.
+    Synchronises with the device."""
+    torch.cuda.synchronize()
+    sums: Dict[str, list] = {}
+    for name, e0, e1 in _timing_events:
+        sums.setdefault(name, []).append(e0.elapsed_time(e1))
+    _timing_events.clear()
+    return {k: sum(v) / len(v) for k, v in sums.items()}
+
+
+class _timed:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _timing_enabled:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+
+    def __exit__(self, *exc):
+        if _timing_enabled:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            _timing_events.append((self.name, self.e0, e1))
+        return False
+
 
 def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
                   gating_output: torch.Tensor, topk: int, renormalize: bool = True,
@@ -116,22 +155,29 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
 
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
-        _C.topk_softmax(ws["topk_weights"], ws["topk_ids"], gating, renormalize=renormalize)
-        _C.moe_align_block_size(ws["topk_ids"], num_experts, BLOCK_SIZE_M, ws["sorted_ids"],
-                                ws["expert_ids"], ws["num_post_pad"], fill_pads=True)
-        _lib.check(lib.b200moe_gather_rows(
-            hidden_states.data_ptr(), ws["a_sorted"].data_ptr(), ws["sorted_ids"].data_ptr(),
-            ws["num_post_pad"].data_ptr(), capacity, num_tokens, hidden, topk, stream),
-            "gather_rows")
-        _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
-            ws["a_sorted"].data_ptr(), w1.data_ptr(), ws["act"].data_ptr(),
-            ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity, num_experts,
-            hidden, inter, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
-        _lib.check(lib.b200moe_grouped_gemm_w2_scale(
-            ws["act"].data_ptr(), w2.data_ptr(), ws["cache3"].data_ptr(),
-            ws["topk_weights"].data_ptr(), ws["sorted_ids"].data_ptr(),
-            ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
-            num_tokens * topk, num_experts, hidden, inter, BLOCK_SIZE_M, stream),
-            "grouped_gemm_w2_scale")
-        _C.moe_sum(ws["cache3"], output)
+        with _timed("topk_softmax"):
+            _C.topk_softmax(ws["topk_weights"], ws["topk_ids"], gating, renormalize=renormalize)
+        with _timed("moe_align_block_size"):
+            _C.moe_align_block_size(ws["topk_ids"], num_experts, BLOCK_SIZE_M, ws["sorted_ids"],
+                                    ws["expert_ids"], ws["num_post_pad"], fill_pads=True)
+        with _timed("gather_rows"):
+            _lib.check(lib.b200moe_gather_rows(
+                hidden_states.data_ptr(), ws["a_sorted"].data_ptr(), ws["sorted_ids"].data_ptr(),
+                ws["num_post_pad"].data_ptr(), capacity, num_tokens, hidden, topk, stream),
+                "gather_rows")
+        with _timed("grouped_gemm_w13_swiglu"):
+            _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
+                ws["a_sorted"].data_ptr(), w1.data_ptr(), ws["act"].data_ptr(),
+                ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity, num_experts,
+                hidden, inter, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
+        with _timed("grouped_gemm_w2_scale"):
+            _lib.check(lib.b200moe_grouped_gemm_w2_scale(
+                ws["act"].data_ptr(), w2.data_ptr(), ws["cache3"].data_ptr(),
+                ws["topk_weights"].data_ptr(), ws["sorted_ids"].data_ptr(),
+                ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
+                num_tokens * topk, num_experts, hidden, inter, BLOCK_SIZE_M, stream),
+                "grouped_gemm_w2_scale")
+        _lib.count_launches(3)
+        with _timed("moe_sum"):
+            _C.moe_sum(ws["cache3"], output)
     return output

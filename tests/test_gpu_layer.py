@@ -44,9 +44,9 @@ def test_grouped_gemm_w13_swiglu(T, H, I, E):
     a_sorted = x[rows].contiguous()
     a_sorted[torch.from_numpy(s) < 0] = 0
     act = torch.full((cap, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    d_a, d_w, d_e, d_n = a_sorted.to(DEV), w13.to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV)
     rc = lib.b200moe_grouped_gemm_w13_swiglu(
-        a_sorted.to(DEV).data_ptr(), w13.to(DEV).data_ptr(), act.data_ptr(),
-        torch.from_numpy(e).to(DEV).data_ptr(), torch.from_numpy(n).to(DEV).data_ptr(), cap, E, H, I,
+        d_a.data_ptr(), d_w.data_ptr(), act.data_ptr(), d_e.data_ptr(), d_n.data_ptr(), cap, E, H, I,
         BLOCK_SIZE_M, torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "w13")
     torch.cuda.synchronize()
@@ -76,10 +76,11 @@ def test_grouped_gemm_w2_scale(T, H, I, E):
     w2 = (torch.randn(E, H, I, generator=g) / I ** 0.5).to(torch.bfloat16)
     tw = torch.rand(T * 2, generator=g)
     out = torch.full((T * 2, H), 9.0, dtype=torch.bfloat16, device=DEV)
+    d_act, d_w, d_tw = act.to(DEV), w2.to(DEV), tw.to(DEV)
+    d_s, d_e, d_n = torch.from_numpy(s).to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV)
     rc = lib.b200moe_grouped_gemm_w2_scale(
-        act.to(DEV).data_ptr(), w2.to(DEV).data_ptr(), out.data_ptr(), tw.to(DEV).data_ptr(),
-        torch.from_numpy(s).to(DEV).data_ptr(), torch.from_numpy(e).to(DEV).data_ptr(),
-        torch.from_numpy(n).to(DEV).data_ptr(), cap, T * 2, E, H, I, BLOCK_SIZE_M,
+        d_act.data_ptr(), d_w.data_ptr(), out.data_ptr(), d_tw.data_ptr(), d_s.data_ptr(),
+        d_e.data_ptr(), d_n.data_ptr(), cap, T * 2, E, H, I, BLOCK_SIZE_M,
         torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "w2")
     torch.cuda.synchronize()

@@ -183,9 +183,10 @@ def test_silu_and_mul(dtype, shape):
     if dtype == torch.float32:
         assert torch.allclose(got, want, rtol=2e-6, atol=1e-7)
     else:
-        # Fast exponential on the device: the rounded SiLU may differ by one unit in the last place.
-        eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
-        assert ((got.float() - want.float()).abs() <= 2 * eps * want.float().abs() + 1e-6).all()
+        # Fast exponential on the device: the rounded SiLU may differ by one unit in the last place,
+        # which the rounded product can turn into two.
+        ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+        assert ((got.float() - want.float()).abs() <= 3 * ulp * want.float().abs() + 1e-6).all()
         assert (got == want).float().mean() > 0.98
 
 
