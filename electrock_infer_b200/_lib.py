@@ -27,6 +27,10 @@ SIGNATURES = {
     "b200moe_align_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "b200moe_align_single_pass_max": (c_int64, []),
     "b200moe_align_max_experts": (c_int, []),
+    "b200moe_align_block_size_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
+                                                 c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                                                 c_int, c_void_p]),
+    "b200moe_align_noalloc_max_numel": (c_int64, []),
     "b200moe_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p]),
     "b200moe_moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int,
                                 c_void_p]),

@@ -13,6 +13,8 @@
 // to a few tens of thousands of ids).  Longer inputs use three launches over segments of
 // kSegment ids: per-segment histogram, a one-CTA scan over segments, and a scatter that re-reads
 // the ids (from L2 at these sizes).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -344,8 +346,68 @@ int run(const void* ids_v, int64_t numel, int E, int bs, int32_t* sorted, int64_
   return check_launch("moe_align_block_size");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the segment counters of the multi-launch path live in a fixed array
+// that is part of the loaded library image on every device, instead of a caller workspace.
+// ---------------------------------------------------------------------------------------------
+constexpr int64_t kStaticMaxIds = 1ll << 24;  // 16 Mi pair indices = 8 Mi tokens at top-2
+constexpr int64_t kStaticScratchInts =
+    (kStaticMaxIds / kSegment) * kMaxExperts + 2 * kMaxExperts + 1;  // 16401 ints, about 64 KiB
+
+static __device__ __align__(256) int32_t g_align_scratch[kStaticScratchInts];
+
+// Device address of g_align_scratch on the current device.  In host code the array's name is only
+// a handle for the runtime, not an address a kernel may use, so the address is looked up once per
+// device (with that device current) and cached.
+int static_scratch(int32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int32_t* cached[kMaxDevices] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "align_block_size_noalloc: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(B200MOE_ERR_UNSUPPORTED, "align_block_size_noalloc: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_align_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(B200MOE_ERR_CUDA, "align_block_size_noalloc: cudaGetSymbolAddress failed: %s",
+                  cudaGetErrorString(e));
+    cached[dev] = static_cast<int32_t*>(ptr);
+  }
+  *out = cached[dev];
+  return B200MOE_OK;
+}
+
 }  // namespace
 }  // namespace b200moe
+
+extern "C" int64_t b200moe_align_noalloc_max_numel(void) { return b200moe::kStaticMaxIds; }
+
+extern "C" int b200moe_align_block_size_noalloc(const void* topk_ids, int ids_dtype, int64_t numel,
+                                                int num_experts, int block_size,
+                                                int32_t* sorted_token_ids, int64_t sorted_capacity,
+                                                int32_t* expert_ids, int64_t expert_ids_capacity,
+                                                int32_t* num_tokens_post_pad,
+                                                int32_t* expert_offsets, int fill_pads,
+                                                b200moe_stream_t stream) {
+  using namespace b200moe;
+  if (numel > kStaticMaxIds)
+    return fail(B200MOE_ERR_SHAPE,
+                "align_block_size_noalloc: numel=%lld exceeds the built-in scratch limit of %lld "
+                "pair indices; use b200moe_align_block_size with a workspace",
+                (long long)numel, (long long)kStaticMaxIds);
+  int32_t* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  // Same validation and the same kernels as the workspace variant; only the scratch differs.
+  return b200moe_align_block_size(topk_ids, ids_dtype, numel, num_experts, block_size,
+                                  sorted_token_ids, sorted_capacity, expert_ids,
+                                  expert_ids_capacity, num_tokens_post_pad, expert_offsets,
+                                  fill_pads, scratch,
+                                  static_cast<size_t>(kStaticScratchInts) * sizeof(int32_t), stream);
+}
 
 extern "C" size_t b200moe_align_workspace_bytes(int64_t numel, int num_experts) {
   using namespace b200moe;

@@ -97,7 +97,7 @@ int b200moe_topk_softmax(float* topk_weights, int32_t* topk_indices, const void*
  *
  * Inputs longer than b200moe_align_single_pass_max() need a workspace of
  * b200moe_align_workspace_bytes() bytes (4-byte aligned device memory); shorter inputs run as
- * one launch and ignore it.  num_experts must be between 1 and 8... see b200moe_align_max_experts().
+ * one launch and ignore it.  num_experts must lie in [1, b200moe_align_max_experts()] (8).
  * Pair indices with an expert outside [0, num_experts) are skipped.
  */
 int b200moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel, int num_experts,
@@ -108,6 +108,38 @@ int b200moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel,
 size_t b200moe_align_workspace_bytes(int64_t numel, int num_experts);
 int64_t b200moe_align_single_pass_max(void);
 int b200moe_align_max_experts(void);
+
+/*
+ * Token alignment for hosts that must not allocate device memory.  No counterpart in the
+ * reference.
+ *
+ * Why it exists: b200moe_align_block_size needs a caller workspace for long inputs.  Some hosts
+ * cannot provide one at call time: an inference server that gave the whole device to a pre-sized
+ * pool at start-up (the reference engine sizes its KV cache from the free memory it finds and
+ * leaves nothing behind), a plain C or cgo/JNI host with no device allocator of its own, or a
+ * latency-critical loop where cudaMalloc would stall the device.  This entry point computes the
+ * same outputs, with the same arguments minus the workspace, and keeps its segment counters in a
+ * fixed array inside the library image (about 64 KiB of device memory on every GPU that loads the
+ * library, held until the process exits).  It calls no cudaMalloc, cudaFree or other allocating
+ * routine.
+ *
+ * Limits and rules:
+ *   - numel <= b200moe_align_noalloc_max_numel() (16 Mi pair indices); larger inputs are rejected
+ *     with B200MOE_ERR_SHAPE and must use the workspace variant.
+ *   - The first call on each device looks up the device address of the built-in array (a runtime
+ *     query, no allocation).  Make that first call during set-up, before any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it has to be zero beforehand (every
+ *     word a call reads is first written by that call), but two calls whose kernels overlap on the
+ *     GPU - different streams without ordering between them - race on it and corrupt each other.
+ *     Calls on one stream, or ordered by events, are safe.
+ */
+int b200moe_align_block_size_noalloc(const void* topk_ids, int ids_dtype, int64_t numel,
+                                     int num_experts, int block_size, int32_t* sorted_token_ids,
+                                     int64_t sorted_capacity, int32_t* expert_ids,
+                                     int64_t expert_ids_capacity, int32_t* num_tokens_post_pad,
+                                     int32_t* expert_offsets, int fill_pads,
+                                     b200moe_stream_t stream);
+int64_t b200moe_align_noalloc_max_numel(void);
 
 /*
  * SwiGLU activation as a stand-alone op: out[r, j] = cast(silu_f32(in[r, j])) * in[r, d + j].
