@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--parallel", choices=["tp", "ep"], default="tp")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=None,
+                    help="override the workload's token count (profiling on a smaller case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -181,6 +183,10 @@ def main():
     if wl.dtype != torch.bfloat16:
         wl = MoEWorkload(wl.name, wl.num_tokens, wl.hidden, wl.inter, wl.num_experts, wl.top_k,
                          torch.bfloat16, wl.seed, wl.logit_bias)
+
+    if args.tokens is not None:
+        wl = MoEWorkload(f"{wl.name}@T={args.tokens}", args.tokens, wl.hidden, wl.inter,
+                         wl.num_experts, wl.top_k, wl.dtype, wl.seed, wl.logit_bias)
 
     if args.impl == "reference":
         run_reference(args, wl)

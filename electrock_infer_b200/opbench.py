@@ -1,0 +1,87 @@
+"""Bandwidth sweep of the HBM-bound ops (router, alignment, combine, stand-alone SwiGLU).
+
+    python -m electrock_infer_b200.opbench [--tokens 1048576 2097152 4194304] [--iters 20]
+
+At the layer's own token counts the router and alignment move well under a megabyte, so a single
+launch is latency-bound; this sweep runs them at 2^20..2^22 tokens, where their HBM rate is
+meaningful.  Buffers are larger than L2 at these sizes except the router/alignment inputs, so an
+L2-sized buffer is overwritten between timed launches.  Prints one JSON line per op and size with
+the algorithmic bytes, the mean CUDA-event time and GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import _C
+
+
+def time_op(fn, iters: int, flush: torch.Tensor) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush.add_(1)  # evict L2 between timed launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, nargs="+", default=[1 << 20, 1 << 21, 1 << 22])
+    ap.add_argument("--combine-tokens", type=int, nargs="+", default=[8192, 16384, 65536])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--hidden", type=int, default=4096)
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device=dev)  # 256 MiB > L2
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def report(op, tokens, nbytes, ms, **kw):
+        print(json.dumps({"op": op, "tokens": tokens, "algorithmic_bytes": nbytes,
+                          "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), **kw}), flush=True)
+
+    for T in args.tokens:
+        logits = torch.randn(T, 8, generator=g, device=dev)
+        w = torch.empty(T, 2, device=dev)
+        ids = torch.empty(T, 2, dtype=torch.int32, device=dev)
+        ms = time_op(lambda: _C.topk_softmax(w, ids, logits, renormalize=True), args.iters, flush)
+        report("topk_softmax", T, T * 48, ms)
+
+        bs = 128
+        cap = 2 * T + 8 * (bs - 1)
+        s = torch.empty(cap, dtype=torch.int32, device=dev)
+        e = torch.zeros((cap + bs - 1) // bs, dtype=torch.int32, device=dev)
+        n = torch.zeros(1, dtype=torch.int32, device=dev)
+        ms = time_op(lambda: _C.moe_align_block_size(ids, 8, bs, s, e, n, fill_pads=True),
+                     args.iters, flush)
+        npp = int(n.item())
+        report("moe_align_block_size", T, 2 * T * 4 + npp * 4 + (npp // bs) * 4 + 4, ms, launches=3)
+
+    H = args.hidden
+    for T in args.combine_tokens:
+        x = torch.randn(T, 2, H, generator=g, device=dev).to(torch.bfloat16)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        ms = time_op(lambda: _C.moe_sum(x, out), args.iters, flush)
+        report("moe_sum", T, T * H * 2 * 3, ms)
+        xi = x.view(T, H, 2)
+        ms = time_op(lambda: _C.moe_sum_efficient(xi, out), args.iters, flush)
+        report("moe_sum_efficient", T, T * H * 2 * 3, ms)
+    for rows, d in ((16384, 14336), (4096, 14336)):
+        x = torch.randn(rows, 2 * d, generator=g, device=dev).to(torch.bfloat16)
+        out = torch.empty(rows, d, dtype=torch.bfloat16, device=dev)
+        ms = time_op(lambda: _C.silu_and_mul(out, x), args.iters, flush)
+        report("silu_and_mul", rows // 2, rows * d * 2 * 3, ms)
+
+
+if __name__ == "__main__":
+    main()
