@@ -36,6 +36,8 @@ SIGNATURES = {
                                 c_void_p]),
     "b200moe_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                     c_int64, c_int, c_void_p]),
+    "b200moe_scatter_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                     c_void_p]),
     "b200moe_grouped_gemm_w13_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_int64, c_int, c_int64, c_int64, c_int,
                                                 c_void_p]),

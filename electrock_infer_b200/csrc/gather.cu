@@ -33,8 +33,47 @@ gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
   }
 }
 
+// dst[index[i], :] = src[i, :] for i < num_rows; entries with an index outside [0, num_dst_rows)
+// are skipped.
+__global__ void __launch_bounds__(kThreads)
+scatter_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                    const int32_t* __restrict__ index, int64_t num_rows, int64_t num_dst_rows,
+                    int row_vecs) {
+  const int group = threadIdx.x / (kThreads / kRowsPerCta);
+  const int t = threadIdx.x % (kThreads / kRowsPerCta);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + group; i < num_rows;
+       i += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
+    const int64_t row = index[i];
+    if (row < 0 || row >= num_dst_rows) continue;
+    const uint4* p = src + i * row_vecs;
+    uint4* d = dst + row * row_vecs;
+    for (int c = t; c < row_vecs; c += kThreads / kRowsPerCta) d[c] = __ldg(p + c);
+  }
+}
+
 }  // namespace
 }  // namespace b200moe
+
+extern "C" int b200moe_scatter_rows(const void* src, void* dst, const int32_t* index,
+                                    int64_t num_rows, int64_t num_dst_rows, int64_t row_elems,
+                                    b200moe_stream_t stream) {
+  using namespace b200moe;
+  if (row_elems <= 0 || row_elems % 8 != 0)
+    return fail(B200MOE_ERR_SHAPE, "scatter_rows: row_elems=%lld must be a positive multiple of 8",
+                (long long)row_elems);
+  if (num_rows < 0 || num_dst_rows < 0) return fail(B200MOE_ERR_SHAPE, "scatter_rows: negative size");
+  if (num_rows == 0) return B200MOE_OK;
+  if (!src || !dst || !index) return fail(B200MOE_ERR_NULL, "scatter_rows: null pointer");
+  if (!aligned_to(src, 16) || !aligned_to(dst, 16))
+    return fail(B200MOE_ERR_ALIGN, "scatter_rows: src and dst must be 16-byte aligned");
+  int64_t grid = ceil_div64(num_rows, kRowsPerCta);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (grid > cap) grid = cap;
+  scatter_rows_kernel<<<static_cast<unsigned>(grid), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, num_rows, num_dst_rows,
+      static_cast<int>(row_elems / 8));
+  return check_launch("scatter_rows");
+}
 
 extern "C" int b200moe_gather_rows(const void* src, void* dst, const int32_t* sorted_token_ids,
                                    const int32_t* num_tokens_post_pad, int64_t sorted_capacity,

@@ -1,0 +1,222 @@
+"""Sharding the MoE layer over the GPUs of one NVLink/NVSwitch box with ``torch.distributed``.
+
+Tensor parallel is what the reference does: ``FusedMoE(tp_size=world, reduce_results=True)`` shards
+the intermediate dimension and all-reduces the combined output (layers/moe/mixtral_moe.py:114-116);
+nothing more is needed for it than the class in ``layers.moe``.
+
+Expert parallel has no counterpart in the reference (its docstring says EP was removed,
+layers/moe/mixtral_moe.py:9-13).  ``ExpertParallelMoE`` keeps ``num_experts / world`` whole experts
+on each rank and a slice of the tokens on each rank:
+
+    route locally -> sort pairs by expert -> exchange per-expert counts (all-to-all)
+    -> exchange rows and routing weights (all-to-all, variable splits)
+    -> local alignment + grouped GEMMs over the rank's experts
+    -> return rows (all-to-all) -> scatter to pair order -> combine
+
+Rows always land in the receiving GPU's own memory (NCCL receive buffers) before any TMA load
+touches them.  Every arithmetic step is the one the single-GPU layer performs on the same row, so
+the result is bit-identical to the single-GPU result for the same tokens.
+
+The exchange logic is written against a small ``ops`` object so that it can be exercised on CPU
+ranks (gloo) in tests with a stand-in ``ops``; the product default is :class:`CudaOps` and nothing
+in this package implements the arithmetic on the CPU.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import _C, _lib
+from .layers.moe.fused_moe import BLOCK_SIZE_M
+
+
+class CudaOps:
+    """The arithmetic steps of the expert-parallel layer on the local GPU (C-ABI calls)."""
+
+    def route(self, logits: torch.Tensor, top_k: int,
+              renormalize: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+        T = logits.shape[0]
+        w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+        _C.topk_softmax(w, ids, logits.contiguous(), renormalize=renormalize)
+        return w, ids
+
+    def sort_pairs_by_expert(self, ids: torch.Tensor,
+                             num_experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Stable order of the flat pair indices by expert, and the count per expert: token
+        alignment with block size 1 (no padding)."""
+        P = ids.numel()
+        dev = ids.device
+        order = torch.empty(max(P, 1), dtype=torch.int32, device=dev)
+        blocks = torch.empty(max(P, 1), dtype=torch.int32, device=dev)
+        npp = torch.empty(1, dtype=torch.int32, device=dev)
+        offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+        _C.moe_align_block_size(ids, num_experts, 1, order, blocks, npp, expert_offsets=offsets)
+        return order[:P], offsets[1:] - offsets[:-1]
+
+    def take_rows(self, src: torch.Tensor, index: torch.Tensor, top_k: int) -> torch.Tensor:
+        """``dst[i] = src[index[i] // top_k]``."""
+        n = index.numel()
+        dst = torch.empty(n, src.shape[1], dtype=src.dtype, device=src.device)
+        if n == 0:
+            return dst
+        count = torch.full((1,), n, dtype=torch.int32, device=src.device)
+        rc = _lib.load().b200moe_gather_rows(
+            src.data_ptr(), dst.data_ptr(), index.data_ptr(), count.data_ptr(), n, src.shape[0],
+            src.shape[1], top_k, torch.cuda.current_stream(src.device).cuda_stream)
+        _lib.check(rc, "gather_rows")
+        _lib.count_launches(1)
+        return dst
+
+    def expert_ffn(self, rows: torch.Tensor, row_expert: torch.Tensor, row_weight: torch.Tensor,
+                   w13: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+        """``y[i] = bf16(row_weight[i] * w2[e] (silu(w1[e] x) * (w3[e] x)))`` with ``e = row_expert[i]``
+        over the local experts: alignment, gather, the two grouped GEMMs."""
+        lib = _lib.load()
+        R, H = rows.shape
+        E, inter = w13.shape[0], w13.shape[1] // 2
+        dev = rows.device
+        out = torch.empty(R, H, dtype=rows.dtype, device=dev)
+        if R == 0:
+            return out
+        cap = R + E * (BLOCK_SIZE_M - 1)
+        nblk = (cap + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M
+        sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
+        expert_ids = torch.zeros(nblk, dtype=torch.int32, device=dev)
+        npp = torch.empty(1, dtype=torch.int32, device=dev)
+        a_sorted = torch.empty(cap, H, dtype=rows.dtype, device=dev)
+        act = torch.empty(cap, inter, dtype=rows.dtype, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _C.moe_align_block_size(row_expert, E, BLOCK_SIZE_M, sorted_ids, expert_ids, npp,
+                                fill_pads=True)
+        _lib.check(lib.b200moe_gather_rows(rows.data_ptr(), a_sorted.data_ptr(),
+                                           sorted_ids.data_ptr(), npp.data_ptr(), cap, R, H, 1,
+                                           stream), "gather_rows")
+        _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
+            a_sorted.data_ptr(), w13.data_ptr(), act.data_ptr(), expert_ids.data_ptr(),
+            npp.data_ptr(), cap, E, H, inter, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
+        _lib.check(lib.b200moe_grouped_gemm_w2_scale(
+            act.data_ptr(), w2.data_ptr(), out.data_ptr(), row_weight.data_ptr(),
+            sorted_ids.data_ptr(), expert_ids.data_ptr(), npp.data_ptr(), cap, R, E, H, inter,
+            BLOCK_SIZE_M, stream), "grouped_gemm_w2_scale")
+        _lib.count_launches(3)
+        return out
+
+    def combine(self, y_back: torch.Tensor, order: torch.Tensor, out: torch.Tensor,
+                top_k: int) -> None:
+        """Puts returned rows back at their pair index and sums each token's ``top_k`` rows."""
+        T, H = out.shape
+        cache = torch.empty(T, top_k, H, dtype=out.dtype, device=out.device)
+        rc = _lib.load().b200moe_scatter_rows(
+            y_back.data_ptr(), cache.data_ptr(), order.data_ptr(), order.numel(), T * top_k, H,
+            torch.cuda.current_stream(out.device).cuda_stream)
+        _lib.check(rc, "scatter_rows")
+        _lib.count_launches(1)
+        _C.moe_sum(cache, out)
+
+
+def split_sizes(counts_per_expert: List[int], ep_size: int) -> List[int]:
+    """Rows this rank sends to every rank: experts are dealt out in contiguous groups."""
+    per = len(counts_per_expert) // ep_size
+    return [sum(counts_per_expert[r * per:(r + 1) * per]) for r in range(ep_size)]
+
+
+def received_row_experts(recv_counts: torch.Tensor, total: int) -> torch.Tensor:
+    """Local expert index (int32) of every received row.  ``recv_counts[s * per + j]`` rows come
+    from source rank ``s`` for local expert ``j``; each source's rows arrive ordered by expert.
+    ``total`` is the known row count, so no device synchronisation is needed."""
+    ep_times_per = recv_counts.numel()
+    return torch.repeat_interleave(
+        torch.arange(ep_times_per, dtype=torch.int32, device=recv_counts.device),
+        recv_counts.long(), output_size=total)
+
+
+class ExpertParallelMoE(nn.Module):
+    """Mixtral experts split across the ranks of ``group``; tokens are data-parallel.
+
+    Parameters hold only the local experts: ``w13_weight [E/ep, 2I, H]``, ``w2_weight [E/ep, H, I]``
+    with the same row layout and ``weight_loader(param, w, shard_id, expert_id)`` signature as
+    ``FusedMoE`` (experts that live elsewhere are ignored by the loader).
+    ``forward(hidden_states [T_local, H], router_logits [T_local, E])`` overwrites and returns
+    ``hidden_states``.
+    """
+
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
+                 params_dtype: Optional[torch.dtype] = None, renormalize: bool = True,
+                 group: Optional[dist.ProcessGroup] = None, ops=None):
+        super().__init__()
+        self.group = group
+        self.ep_size = dist.get_world_size(group)
+        self.ep_rank = dist.get_rank(group)
+        if num_experts % self.ep_size != 0:
+            raise ValueError(f"num_experts ({num_experts}) must be divisible by the expert-parallel "
+                             f"size ({self.ep_size})")
+        self.num_experts = num_experts
+        self.experts_per_rank = num_experts // self.ep_size
+        self.first_expert = self.ep_rank * self.experts_per_rank
+        self.top_k = top_k
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.renormalize = renormalize
+        self.params_dtype = params_dtype or torch.get_default_dtype()
+        self.ops = ops if ops is not None else CudaOps()
+        self.w13_weight = nn.Parameter(torch.empty(
+            self.experts_per_rank, 2 * intermediate_size, hidden_size, dtype=self.params_dtype),
+            requires_grad=False)
+        self.w2_weight = nn.Parameter(torch.empty(
+            self.experts_per_rank, hidden_size, intermediate_size, dtype=self.params_dtype),
+            requires_grad=False)
+        self.w13_weight.weight_loader = self.weight_loader
+        self.w2_weight.weight_loader = self.weight_loader
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, shard_id: str,
+                      expert_id: int) -> None:
+        local = expert_id - self.first_expert
+        if not 0 <= local < self.experts_per_rank:
+            return
+        inter = self.intermediate_size
+        if shard_id == "w1":
+            param.data[local, :inter].copy_(loaded_weight)
+        elif shard_id == "w3":
+            param.data[local, inter:].copy_(loaded_weight)
+        elif shard_id == "w2":
+            param.data[local].copy_(loaded_weight)
+        else:
+            raise ValueError(f"unknown shard_id: {shard_id}")
+
+    def _all_to_all(self, send: torch.Tensor, send_splits: List[int],
+                    recv_splits: List[int]) -> torch.Tensor:
+        recv = torch.empty((sum(recv_splits),) + tuple(send.shape[1:]), dtype=send.dtype,
+                           device=send.device)
+        dist.all_to_all_single(recv, send.contiguous(), recv_splits, send_splits, group=self.group)
+        return recv
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        ops, ep, per = self.ops, self.ep_size, self.experts_per_rank
+        dev = hidden_states.device
+        weights, ids = ops.route(router_logits, self.top_k, self.renormalize)
+        order, counts = ops.sort_pairs_by_expert(ids, self.num_experts)
+
+        # Per-expert counts: rank r receives, from every source, the counts of its own experts.
+        recv_counts = torch.empty(ep * per, dtype=counts.dtype, device=dev)
+        dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.group)
+        both = torch.cat([counts, recv_counts]).cpu()  # the one host synchronisation of the layer
+        send_counts = both[: self.num_experts].tolist()
+        recv_counts_host = both[self.num_experts:].view(ep, per)
+        send_splits = split_sizes(send_counts, ep)
+        recv_splits = [int(recv_counts_host[s].sum()) for s in range(ep)]
+
+        send_rows = ops.take_rows(hidden_states, order, self.top_k)
+        send_w = weights.reshape(-1)[order.long()]
+        recv_rows = self._all_to_all(send_rows, send_splits, recv_splits)
+        recv_w = self._all_to_all(send_w, send_splits, recv_splits)
+        row_expert = received_row_experts(recv_counts, sum(recv_splits)) % per
+
+        y = ops.expert_ffn(recv_rows, row_expert, recv_w.contiguous(), self.w13_weight,
+                           self.w2_weight)
+        y_back = self._all_to_all(y, recv_splits, send_splits)
+        ops.combine(y_back, order, hidden_states, self.top_k)
+        return hidden_states

@@ -178,6 +178,15 @@ int b200moe_gather_rows(const void* src, void* dst, const int32_t* sorted_token_
                         b200moe_stream_t stream);
 
 /*
+ * Row scatter, the inverse of the gather: dst[index[i], :] = src[i, :] for i < num_rows (bf16 rows,
+ * row_elems % 8 == 0); indices outside [0, num_dst_rows) are skipped.  Used by the expert-parallel
+ * return path to put expert outputs back at their pair index, the addressing of the reference's
+ * grouped-GEMM store (layers/moe/fused_moe.py:123-125).
+ */
+int b200moe_scatter_rows(const void* src, void* dst, const int32_t* index, int64_t num_rows,
+                         int64_t num_dst_rows, int64_t row_elems, b200moe_stream_t stream);
+
+/*
  * Grouped expert GEMM 1 with the SwiGLU epilogue (tcgen05 / TMEM / TMA):
  *   act[s, j] = bf16( silu(g) * u ),  g = sum_k a[s, k] * w13[e, j, k],
  *                                     u = sum_k a[s, k] * w13[e, inter + j, k],

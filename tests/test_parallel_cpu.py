@@ -1,0 +1,146 @@
+"""Multi-rank host logic on CPU ranks (gloo, world size 2): the expert-parallel exchange (counts,
+variable-split all-to-alls, return path, un-permutation) and the tensor-parallel all-reduce branch
+of FusedMoE.forward.  The arithmetic is supplied by oracle-based stand-ins defined here; the
+product's own arithmetic only exists on the GPU."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+REPO = Path(__file__).resolve().parent.parent
+if str(REPO) not in sys.path:
+    sys.path.insert(0, str(REPO))
+
+from electrock_infer_b200.synthetic import MoEWorkload, make_inputs  # noqa: E402
+
+WORLD = 2
+
+
+class OracleOps:
+    """CPU stand-in for parallel.CudaOps built from the oracle."""
+
+    def route(self, logits, top_k, renormalize):
+        from oracle import moe_oracle
+        return moe_oracle.router_ref(logits, top_k, renormalize)
+
+    def sort_pairs_by_expert(self, ids, num_experts):
+        flat = ids.reshape(-1).long()
+        order = torch.sort(flat, stable=True).indices.to(torch.int32)
+        return order, torch.bincount(flat, minlength=num_experts).to(torch.int32)
+
+    def take_rows(self, src, index, top_k):
+        return src[index.long() // top_k].contiguous()
+
+    def expert_ffn(self, rows, row_expert, row_weight, w13, w2):
+        inter = w13.shape[1] // 2
+        out = torch.zeros(rows.shape[0], rows.shape[1])
+        for e in range(w13.shape[0]):
+            m = row_expert == e
+            if m.any():
+                x = rows[m].float()
+                h = torch.nn.functional.silu(x @ w13[e, :inter].float().T) * (x @ w13[e, inter:].float().T)
+                out[m] = (h @ w2[e].float().T) * row_weight[m].unsqueeze(1)
+        return out.to(rows.dtype)
+
+    def combine(self, y_back, order, out, top_k):
+        cache = torch.zeros(out.shape[0] * top_k, out.shape[1], dtype=y_back.dtype)
+        cache[order.long()] = y_back
+        out.copy_(cache.view(out.shape[0], top_k, -1).float().sum(1).to(out.dtype))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _init(rank, port):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+
+
+def _ep_worker(rank, port, skew, result_dir):
+    from electrock_infer_b200.parallel import ExpertParallelMoE
+    from oracle import moe_oracle
+    _init(rank, port)
+    bias = (3, 2, 1, 0, 0, -1, -2, -9) if skew else None
+    wl = MoEWorkload("ep", 70, 32, 64, dtype=torch.float32, seed=17, logit_bias=bias)
+    full = make_inputs(wl)
+    per = wl.num_experts // WORLD
+    layer = ExpertParallelMoE(wl.num_experts, 2, wl.hidden, wl.inter, params_dtype=torch.float32,
+                              ops=OracleOps())
+    for e in range(wl.num_experts):  # the loader keeps only this rank's experts
+        layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter], "w1", e)
+        layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:], "w3", e)
+        layer.weight_loader(layer.w2_weight, full["w2"][e], "w2", e)
+    assert torch.equal(layer.w13_weight.data, full["w13"][rank * per:(rank + 1) * per])
+    # Uneven token split: rank 0 gets 41 tokens, rank 1 gets 29.
+    lo, hi = (0, 41) if rank == 0 else (41, 70)
+    x = full["x"][lo:hi].clone()
+    out = layer(x, full["logits"][lo:hi])
+    assert out.data_ptr() == x.data_ptr()
+    want = moe_oracle.moe_block_ref(full["x"], full["w13"], full["w2"], full["logits"])[lo:hi]
+    err = (out - want).abs().max().item()
+    torch.save({"err": err, "rows": out.shape[0]}, os.path.join(result_dir, f"ep{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("skew", [False, True])
+def test_expert_parallel_exchange_on_gloo(tmp_path, skew):
+    mp.spawn(_ep_worker, args=(_free_port(), skew, str(tmp_path)), nprocs=WORLD, join=True)
+    for rank, rows in ((0, 41), (1, 29)):
+        r = torch.load(tmp_path / f"ep{rank}.pt")
+        assert r["rows"] == rows and r["err"] < 1e-4, r
+
+
+def _tp_worker(rank, port, result_dir):
+    from electrock_infer_b200.layers.moe import FusedMoE, mixtral_moe
+    from oracle import moe_oracle
+    _init(rank, port)
+    wl = MoEWorkload("tp", 33, 32, 64, dtype=torch.float32, seed=19)
+    full = make_inputs(wl)
+
+    def cpu_fused_experts(hidden_states, w1, w2, gating_output, topk, renormalize, inplace,
+                          activation):
+        out = moe_oracle.moe_block_ref(hidden_states, w1, w2, gating_output, topk, renormalize)
+        hidden_states.copy_(out)
+        return hidden_states
+
+    mixtral_moe.fused_experts = cpu_fused_experts  # this process only
+    layer = FusedMoE(wl.num_experts, 2, wl.hidden, wl.inter, tp_size=WORLD,
+                     params_dtype=torch.float32, reduce_results=True)
+    assert layer.tp_rank == rank and layer.intermediate_size_per_partition == wl.inter // WORLD
+    for e in range(wl.num_experts):
+        layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter], "w1", e)
+        layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:], "w3", e)
+        layer.weight_loader(layer.w2_weight, full["w2"][e], "w2", e)
+    shard = make_inputs(wl, inter_slice=slice(rank * 32, (rank + 1) * 32))
+    assert torch.equal(layer.w13_weight.data, shard["w13"]) and torch.equal(layer.w2_weight.data, shard["w2"])
+    x = full["x"].clone()
+    out = layer(x, full["logits"])
+    want = moe_oracle.moe_block_ref(full["x"], full["w13"], full["w2"], full["logits"])
+    torch.save({"err": (out - want).abs().max().item(), "alias": out.data_ptr() == x.data_ptr()},
+               os.path.join(result_dir, f"tp{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_all_reduce_on_gloo(tmp_path):
+    mp.spawn(_tp_worker, args=(_free_port(), str(tmp_path)), nprocs=WORLD, join=True)
+    for rank in range(WORLD):
+        r = torch.load(tmp_path / f"tp{rank}.pt")
+        assert r["alias"] and r["err"] < 1e-4, r
+
+
+def test_split_sizes_and_row_experts():
+    from electrock_infer_b200.parallel import received_row_experts, split_sizes
+    assert split_sizes([3, 0, 2, 5, 1, 1, 0, 4], 2) == [10, 6]
+    assert split_sizes([3, 0, 2, 5, 1, 1, 0, 4], 8) == [3, 0, 2, 5, 1, 1, 0, 4]
+    counts = torch.tensor([2, 0, 1, 3], dtype=torch.int32)  # 2 sources x 2 local experts
+    rows = received_row_experts(counts, 6) % 2
+    assert rows.tolist() == [0, 0, 0, 1, 1, 1] and rows.dtype == torch.int32
