@@ -292,31 +292,102 @@ align_scan_kernel(int32_t* __restrict__ seg_counts, int64_t num_segments, int nu
                         expert_ids, fill_pads, threadIdx.x, kThreads);
 }
 
+// Scatter of one segment.  The ids are read once and kept in registers; ranks inside the segment
+// are resolved in shared memory, so that each expert's share of the segment leaves the SM as one
+// contiguous run of 4-byte-coalesced stores instead of 4-byte stores scattered over eight runs.
 template <typename T>
 __global__ void __launch_bounds__(kSegThreads)
 align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
                      const int32_t* __restrict__ seg_prefix, const int32_t* __restrict__ meta,
                      int32_t* __restrict__ sorted) {
-  __shared__ int s_cnt[kSegWarps][kMaxExperts];
+  constexpr int kIdsPerWarp = kSegment / kSegWarps;          // 1024
+  constexpr int kSteps = kIdsPerWarp / kIdsPerWarpStep;      // 8
+  __shared__ int s_cnt[kSegWarps][kMaxExperts];  // per-warp counts, then exclusive prefix over warps
+  __shared__ int s_base[kMaxExperts + 1];        // start of each expert's run inside the segment
+  __shared__ int s_dst[kMaxExperts];             // output slot of the first element of each run
+  __shared__ int32_t s_sorted[kSegment];
+
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t seg_begin = static_cast<int64_t>(blockIdx.x) * kSegment;
-  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * (kSegment / kSegWarps), numel);
-  const int64_t end = min(begin + kSegment / kSegWarps, numel);
+  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * kIdsPerWarp, numel);
+  const int64_t end = min(begin + kIdsPerWarp, numel);
+
+  int e[kSteps][4];
+  uint64_t excl[kSteps];
   int cnt[kMaxExperts];
-  warp_count<T>(ids, begin, end, numel, num_experts, lane, cnt);
+#pragma unroll
+  for (int x = 0; x < kMaxExperts; ++x) cnt[x] = 0;
+#pragma unroll
+  for (int st = 0; st < kSteps; ++st) {
+    const int64_t first = begin + st * kIdsPerWarpStep + lane * kIdsPerLane;
+    load_ids4<T>(ids, first, end, num_experts, e[st]);
+    const uint64_t mine = pack_counts(e[st]);
+    const uint64_t incl = warp_inclusive_scan(mine, lane);
+    excl[st] = incl - mine;
+    const uint64_t total = __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) cnt[x] += byte_of(total, x);
+  }
   if (lane == 0) {
 #pragma unroll
     for (int x = 0; x < kMaxExperts; ++x) s_cnt[warp][x] = cnt[x];
   }
   __syncthreads();
+  if (threadIdx.x < kMaxExperts) {
+    int acc = 0;
+    for (int w = 0; w < kSegWarps; ++w) {
+      const int c = s_cnt[w][threadIdx.x];
+      s_cnt[w][threadIdx.x] = acc;
+      acc += c;
+    }
+    s_base[threadIdx.x + 1] = acc;  // count for now; turned into offsets below
+    s_dst[threadIdx.x] = meta[threadIdx.x] +
+                         seg_prefix[static_cast<int64_t>(blockIdx.x) * kMaxExperts + threadIdx.x];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_base[0] = 0;
+    for (int x = 0; x < kMaxExperts; ++x) s_base[x + 1] += s_base[x];
+  }
+  __syncthreads();
+
+  // Rank inside the segment -> shared memory.
   int start[kMaxExperts];
 #pragma unroll
-  for (int x = 0; x < kMaxExperts; ++x) {
-    int acc = meta[x] + seg_prefix[static_cast<int64_t>(blockIdx.x) * kMaxExperts + x];
-    for (int w = 0; w < warp; ++w) acc += s_cnt[w][x];
-    start[x] = acc;
+  for (int x = 0; x < kMaxExperts; ++x) start[x] = s_base[x] + s_cnt[warp][x];
+#pragma unroll
+  for (int st = 0; st < kSteps; ++st) {
+    const int first = static_cast<int>(begin - seg_begin) + st * kIdsPerWarpStep + lane * kIdsPerLane;
+    uint64_t ex = excl[st];
+    uint64_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int x = e[st][j];
+      if (x >= 0) {
+        int sx = 0;
+#pragma unroll
+        for (int y = 0; y < kMaxExperts; ++y)
+          if (y == x) sx = start[y];
+        s_sorted[sx + byte_of(ex, x)] = first + j;
+        ex += 1ull << (8 * x);
+        mine += 1ull << (8 * x);
+      }
+    }
+    const uint64_t total = __shfl_sync(0xffffffffu, excl[st] + mine, 31);
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) start[x] += byte_of(total, x);
   }
-  warp_scatter<T>(ids, begin, end, numel, num_experts, lane, start, sorted);
+  __syncthreads();
+
+  // Contiguous runs -> global memory.
+  const int seg_count = s_base[kMaxExperts];
+  const int32_t seg_first = static_cast<int32_t>(seg_begin);
+  for (int i = threadIdx.x; i < seg_count; i += kSegThreads) {
+    int x = 0;
+#pragma unroll
+    for (int y = 1; y < kMaxExperts; ++y) x += (i >= s_base[y]) ? 1 : 0;
+    sorted[s_dst[x] + (i - s_base[x])] = seg_first + s_sorted[i];
+  }
 }
 
 template <typename T>

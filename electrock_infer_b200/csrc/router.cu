@@ -102,20 +102,26 @@ topk_softmax_kernel(const T* __restrict__ logits, float* __restrict__ weights,
     // merge when NaNs are present.  Keep indices in range.
     if (m2.i < 0) m2.i = (m1.i == 0) ? 1 : 0;
 
-    // Softmax denominator: sum over all eight of exp(l - max), each half summed in index order.
-    const float mx = m1.v;
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) s += expf(v[r][j] - mx);
-    const float so = __shfl_xor_sync(0xffffffffu, s, 1);
-    const float sum = half ? (so + s) : (s + so);  // low half first on both lanes
-
-    float p1 = expf(m1.v - mx) / sum;
-    float p2 = expf(m2.v - mx) / sum;
+    // Probabilities.  exp(l1 - max) is exactly 1, so only the runner-up needs an exponential.
+    // The fast exponential (ex2.approx after a multiply) is accurate to a few 1e-7 here, well
+    // inside the 1e-6 the routing weights are held to.
+    const float e2 = __expf(m2.v - m1.v);
+    float p1, p2;
     if (renormalize) {
-      const float d = p1 + p2;
-      p1 = p1 / d;
-      p2 = p2 / d;
+      // p1 / (p1 + p2) with the common softmax denominator cancelled: no row sum is needed.
+      const float inv = 1.0f / (1.0f + e2);
+      p1 = inv;
+      p2 = e2 * inv;
+    } else {
+      // Softmax denominator: each half summed in index order, low half first on both lanes.
+      const float mx = m1.v;
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s += __expf(v[r][j] - mx);
+      const float so = __shfl_xor_sync(0xffffffffu, s, 1);
+      const float inv = 1.0f / (half ? (so + s) : (s + so));
+      p1 = inv;
+      p2 = e2 * inv;
     }
     if (row < num_tokens) {
       if (half == 0) {

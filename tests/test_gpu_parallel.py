@@ -1,0 +1,89 @@
+"""Tensor- and expert-parallel layer on 2 GPUs over NCCL, compared with the single-GPU layer and
+the CPU oracle.  Skipped on a box with fewer than two GPUs."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+REPO = Path(__file__).resolve().parent.parent
+if str(REPO) not in sys.path:
+    sys.path.insert(0, str(REPO))
+
+from electrock_infer_b200.synthetic import MoEWorkload, make_inputs  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+WORLD = 2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, port, mode, result_dir):
+    from electrock_infer_b200 import _lib
+    from electrock_infer_b200.layers.moe import FusedMoE, fused_experts
+    from electrock_infer_b200.parallel import ExpertParallelMoE
+    from oracle import moe_oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+    wl = MoEWorkload("par", 600, 512, 1024, seed=23, logit_bias=(2, 1, 0.5, 0, 0, -0.5, -1, -2))
+    full = make_inputs(wl)
+    want = moe_oracle.moe_block_ref(full["x"], full["w13"], full["w2"], full["logits"])
+    single = fused_experts(full["x"].to(dev), full["w13"].to(dev), full["w2"].to(dev),
+                           full["logits"].to(dev), 2, inplace=False)
+    res = {}
+    if mode == "tp":
+        layer = FusedMoE(8, 2, wl.hidden, wl.inter, tp_size=WORLD, params_dtype=torch.bfloat16,
+                         reduce_results=True).to(dev)
+        for e in range(8):
+            layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
+            layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
+            layer.weight_loader(layer.w2_weight, full["w2"][e].to(dev), "w2", e)
+        x = full["x"].to(dev).clone()
+        out = layer(x, full["logits"].to(dev))
+        torch.cuda.synchronize()
+        res["alias"] = out.data_ptr() == x.data_ptr()
+        res["stats"] = moe_oracle.error_stats(out.cpu().float(), want)
+        res["vs_single"] = moe_oracle.error_stats(out.cpu().float(), single.cpu().float())
+    else:
+        layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16).to(dev)
+        for e in range(8):
+            layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
+            layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
+            layer.weight_loader(layer.w2_weight, full["w2"][e].to(dev), "w2", e)
+        lo, hi = (0, 350) if rank == 0 else (350, 600)  # uneven token split
+        x = full["x"][lo:hi].to(dev).clone()
+        out = layer(x, full["logits"][lo:hi].to(dev))
+        torch.cuda.synchronize()
+        res["alias"] = out.data_ptr() == x.data_ptr()
+        res["stats"] = moe_oracle.error_stats(out.cpu().float(), want[lo:hi])
+        res["bit_exact_vs_single"] = bool(torch.equal(out, single[lo:hi]))
+    res["gemm_status"] = _lib.load().b200moe_gemm_device_status(1)
+    torch.save(res, os.path.join(result_dir, f"{mode}{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["tp", "ep"])
+def test_two_gpu_layer(tmp_path, mode):
+    if torch.cuda.device_count() < WORLD:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_worker, args=(_free_port(), mode, str(tmp_path)), nprocs=WORLD, join=True)
+    for rank in range(WORLD):
+        r = torch.load(tmp_path / f"{mode}{rank}.pt")
+        assert r["alias"] and r["gemm_status"] == 0, r
+        assert r["stats"]["max_abs"] <= 3e-2 and r["stats"]["rel_fro"] <= 1e-2, r
+        if mode == "ep":
+            assert r["bit_exact_vs_single"], "expert-parallel rows must equal the single-GPU rows"
+        else:
+            # TP sums two bf16-rounded partial outputs: close to, not identical with, one GPU.
+            assert r["vs_single"]["rel_fro"] <= 1e-2, r
