@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--parallel", choices=["tp", "ep"], default="tp")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--block-m", type=int, default=None, choices=[128, 256],
+                    help="force the M tile of the grouped GEMMs (default: chosen by batch size)")
     ap.add_argument("--tokens", type=int, default=None,
                     help="override the workload's token count (profiling on a smaller case)")
     args = ap.parse_args()
@@ -200,6 +202,8 @@ def main():
     from electrock_infer_b200.layers.moe import FusedMoE
     from electrock_infer_b200.layers.moe import fused_moe as fm
 
+    if args.block_m is not None:
+        fm.FORCE_BLOCK_M = args.block_m
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -380,6 +384,7 @@ def main():
         "cpu_baseline": cpu_baseline,
         "clocks": clocks,
         "kernel_ms": kernels,
+        "block_m": fm.choose_block_m(tokens_local, wl.top_k, E),
         "layer_tflops": wl.flops / max(world, 1) / (ms_per_step * 1e-3) / 1e12 if layer_cls is None
         else wl.flops / world / (ms_per_step * 1e-3) / 1e12,
         **extra,

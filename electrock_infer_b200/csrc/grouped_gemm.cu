@@ -431,6 +431,304 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
+// ================================================================================================
+// Two-CTA variant (tcgen05 cta_group::2): a cluster of two CTAs on neighbouring SMs computes one
+// 256 x 256 tile.  Each CTA stages its own 128 A rows and one half of the B tile (128 of the 256
+// accumulator columns' weight rows), the leader CTA issues M = 256 MMAs that read both CTAs'
+// shared memory, and each CTA's TMEM receives the 256 accumulator columns of its own 128 rows.
+// Per SM and K step this moves 32 KiB through L2 and shared memory instead of 48 KiB.
+//
+// Barriers: full[s] lives in the leader only (armed by the leader's producer with the bytes of
+// both CTAs; both producers' TMA loads complete on it).  empty[s] and tmem_full[a] exist in both
+// CTAs and are released by the leader's tcgen05.commit, issued once per CTA.  tmem_empty[a] lives
+// in the leader and collects the epilogue warps of both CTAs.  No load uses cluster multicast.
+// ================================================================================================
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = kBlockM * kBlockK * 2;          // 16384: this CTA's 128 A rows
+constexpr int kPairBBytes = (kBlockN / 2) * kBlockK * 2;    // 16384: this CTA's half of B
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;  // 32768
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kSmemAlignSlack;
+constexpr int kPairBlockM = 2 * kBlockM;                    // rows per tile of the pair
+// Instruction descriptor: as kInstrDesc with M = 256 (128 rows in each CTA).
+constexpr uint32_t kPairInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                    (static_cast<uint32_t>(kBlockN >> 3) << 17) |
+                                    (static_cast<uint32_t>(kPairBlockM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;"
+               ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0),
+      "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at shared::cluster address `bar` once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+
+template <int kMode>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[kPairStages], empty_bar[kPairStages], tmem_full_bar[2],
+      tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_blk_cnt[kMaxExperts];
+  __shared__ int s_blk_off[kMaxExperts + 1];
+  __shared__ int s_abort;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + kSmemAlignSlack - 1) &
+      ~static_cast<uintptr_t>(kSmemAlignSlack - 1));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();   // 0 = leader
+  const uint32_t peer_rank = cta_rank ^ 1u;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs_grid = gridDim.x >> 1;
+
+  // ------------------------------------------------------------------ prologue
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 2 * kEpilogueWarps);
+    }
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (threadIdx.x < kMaxExperts) s_blk_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  long long npp = *p.npp;
+  if (npp > p.capacity) npp = p.capacity;
+  const int num_blocks = static_cast<int>(npp / kPairBlockM);
+  for (int b = threadIdx.x; b < num_blocks; b += kThreads) {
+    const int e = p.expert_ids[b];
+    if (e >= 0 && e < p.num_experts) atomicAdd(&s_blk_cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.num_experts; ++e) {
+      s_blk_off[e] = acc;
+      acc += s_blk_cnt[e];
+    }
+    s_blk_off[p.num_experts] = acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const long long total_tiles = static_cast<long long>(s_blk_off[p.num_experts]) * p.n_tiles;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = pair_id; ok && tile < total_tiles; tile += num_pairs_grid) {
+        const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
+        const int a_row = c.m_block * kPairBlockM + static_cast<int>(cta_rank) * kBlockM;
+        // This CTA's half of the B tile: for w13 the leader holds the gate rows and the peer the
+        // matching up rows; for w2 consecutive halves of 128 output columns.
+        const int b_row = c.expert * p.b_rows_per_expert +
+                          (kMode == kW13 ? c.n_tile * (kBlockN / 2) + static_cast<int>(cta_rank) * p.inter
+                                         : c.n_tile * kBlockN + static_cast<int>(cta_rank) * (kBlockN / 2));
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x111)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kPairStageBytes;
+          uint8_t* sb = sa + kPairABytes;
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          tma_load_2d_pair(sa, &tmap_a, full_leader, kb * kBlockK, a_row);
+          tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBlockK, b_row);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && cta_rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long it = 0;
+      for (long long tile = pair_id; ok && tile < total_tiles; tile += num_pairs_grid, ++it) {
+        const int acc = static_cast<int>(it & 1);
+        const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, 0x211)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x212)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint32_t sb = sa + kPairABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * kUmmaK * 2);
+            const uint64_t bdesc = make_smem_desc(sb + k * kUmmaK * 2);
+            umma_bf16_pair(tmem_d, adesc, bdesc, kPairInstrDesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          umma_commit_pair(map_to_cta(eb, 0));
+          umma_commit_pair(map_to_cta(eb, 1));
+          if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {
+          const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
+          umma_commit_pair(map_to_cta(fb, 0));
+          umma_commit_pair(map_to_cta(fb, 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const int row_in_cta = quarter * 32 + lane;
+    bool ok = true;
+    long long it = 0;
+    for (long long tile = pair_id; ok && tile < total_tiles; tile += num_pairs_grid, ++it) {
+      const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
+      const int acc = static_cast<int>(it & 1);
+      const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+      const long long slot = static_cast<long long>(c.m_block) * kPairBlockM +
+                             static_cast<long long>(cta_rank) * kBlockM + row_in_cta;
+      int good = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, 0x311) ? 1 : 0;
+      good = __all_sync(0xffffffffu, good);
+      if (!good) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(acc * kBlockN);
+      if (kMode == kW13) {
+        __nv_bfloat16* dst = p.out + slot * p.out_ld + static_cast<long long>(c.n_tile) * (kBlockN / 2);
+#pragma unroll 1
+        for (int ch = 0; ch < (kBlockN / 2) / 32; ++ch) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + ch * 32, g);
+          tmem_ld_32x32(taddr + kBlockN / 2 + ch * 32, u);
+          tmem_ld_wait();
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+            const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            const float a0 = g0 / (1.0f + __expf(-g0)) * u0;
+            const float a1 = g1 / (1.0f + __expf(-g1)) * u1;
+            o[j] = pack_bf16(a0, a1);
+          }
+          uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            d4[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        }
+      } else {
+        const int pair = p.sorted[slot];
+        const bool live = pair >= 0 && pair < p.num_pairs;
+        const float w = live ? p.topk_weights[pair] : 0.f;
+        __nv_bfloat16* dst = p.out + static_cast<long long>(live ? pair : 0) * p.out_ld +
+                             static_cast<long long>(c.n_tile) * kBlockN;
+#pragma unroll 1
+        for (int ch = 0; ch < kBlockN / 32; ++ch) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + ch * 32, v);
+          tmem_ld_wait();
+          if (live) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[8 * q + 0]) * w, __uint_as_float(v[8 * q + 1]) * w);
+              o.y = pack_bf16(__uint_as_float(v[8 * q + 2]) * w, __uint_as_float(v[8 * q + 3]) * w);
+              o.z = pack_bf16(__uint_as_float(v[8 * q + 4]) * w, __uint_as_float(v[8 * q + 5]) * w);
+              o.w = pack_bf16(__uint_as_float(v[8 * q + 6]) * w, __uint_as_float(v[8 * q + 7]) * w);
+              d4[q] = o;
+            }
+          }
+        }
+      }
+      // Hand the accumulator back: every epilogue warp of both CTAs arrives at the leader.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < (1ll << 22)) {}
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be signalling this CTA's barriers until here
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  (void)peer_rank;
+}
+
 // ------------------------------------------------------------------------------------ host side
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -477,16 +775,29 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cu
   return check_launch("grouped_gemm");
 }
 
+template <int kMode>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+  const cudaError_t attr_err = cudaFuncSetAttribute(
+      grouped_gemm_pair_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+  if (attr_err != cudaSuccess)
+    return fail(B200MOE_ERR_CUDA, "grouped_gemm: cannot reserve %d bytes of shared memory: %s",
+                kPairSmemBytes, cudaGetErrorString(attr_err));
+  const int grid = sm_count() & ~1;  // whole clusters of two CTAs
+  grouped_gemm_pair_kernel<kMode><<<grid, kThreads, kPairSmemBytes, st>>>(ta, tb, p);
+  return check_launch("grouped_gemm (2-CTA)");
+}
+
 int check_common(const char* name, int num_experts, int64_t hidden, int64_t inter, int block_m,
                  int64_t capacity) {
-  if (block_m != kBlockM)
-    return fail(B200MOE_ERR_SHAPE, "%s: block_m must be %d, got %d", name, kBlockM, block_m);
+  if (block_m != kBlockM && block_m != kPairBlockM)
+    return fail(B200MOE_ERR_SHAPE, "%s: block_m must be %d or %d, got %d", name, kBlockM,
+                kPairBlockM, block_m);
   if (num_experts < 1 || num_experts > kMaxExperts)
     return fail(B200MOE_ERR_SHAPE, "%s: num_experts=%d, supported 1..%d", name, num_experts, kMaxExperts);
   if (hidden <= 0 || inter <= 0 || capacity < 0)
     return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld inter=%lld capacity=%lld", name, (long long)hidden,
                 (long long)inter, (long long)capacity);
-  if (capacity > 0x7fffffffLL - kBlockM) return fail(B200MOE_ERR_SHAPE, "%s: capacity too large", name);
+  if (capacity > 0x7fffffffLL - kPairBlockM) return fail(B200MOE_ERR_SHAPE, "%s: capacity too large", name);
   return B200MOE_OK;
 }
 
@@ -507,7 +818,7 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   if (inter % (kBlockN / 2) != 0)
     return fail(B200MOE_ERR_SHAPE, "%s: intermediate size %lld must be a multiple of %d", name,
                 (long long)inter, kBlockN / 2);
-  if (sorted_capacity < kBlockM) return B200MOE_OK;  // no complete block can exist
+  if (sorted_capacity < block_m) return B200MOE_OK;  // no complete block can exist
   if (!a_sorted || !w13 || !act || !expert_ids || !num_tokens_post_pad)
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(a_sorted, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16))
@@ -528,6 +839,7 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   p.b_rows_per_expert = static_cast<int>(2 * inter);
   p.inter = static_cast<int>(inter);
   p.out_ld = inter;
+  if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
 }
 
@@ -548,14 +860,16 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   if (hidden % kBlockN != 0)
     return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld must be a multiple of %d", name, (long long)hidden, kBlockN);
   if (num_pairs < 0) return fail(B200MOE_ERR_SHAPE, "%s: num_pairs=%lld", name, (long long)num_pairs);
-  if (sorted_capacity < kBlockM || num_pairs == 0) return B200MOE_OK;
+  if (sorted_capacity < block_m || num_pairs == 0) return B200MOE_OK;
   if (!act || !w2 || !out || !topk_weights || !sorted_token_ids || !expert_ids || !num_tokens_post_pad)
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16) || !aligned_to(out, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
   CUtensorMap ta, tb;
   if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
-  if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter, kBlockN, name))
+  // The two-CTA kernel fetches the B tile as two boxes of 128 rows, one per CTA.
+  if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter,
+                         block_m == kPairBlockM ? kBlockN / 2 : kBlockN, name))
     return rc;
   GemmParams p{};
   p.expert_ids = expert_ids;
@@ -571,6 +885,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   p.b_rows_per_expert = static_cast<int>(hidden);
   p.inter = 0;
   p.out_ld = hidden;
+  if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
 }
 

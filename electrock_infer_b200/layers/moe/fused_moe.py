@@ -18,7 +18,20 @@ import torch
 from ... import _C, _lib
 
 # Rows per M tile of the tensor-core kernels; token alignment pads every expert to this.
+# 128 rows: one CTA per tile.  256 rows: a pair of CTAs (tcgen05 cta_group::2) per tile, which moves
+# a third less data per FLOP and wins once experts have many rows; it pads more, so small batches
+# keep 128.
 BLOCK_SIZE_M = 128
+PAIR_BLOCK_SIZE_M = 256
+PAIR_MIN_PAIRS_PER_EXPERT = 512
+FORCE_BLOCK_M = None  # set to 128 or 256 to override the choice (benchmarks, tests)
+
+
+def choose_block_m(num_tokens: int, topk: int, num_experts: int) -> int:
+    if FORCE_BLOCK_M is not None:
+        return FORCE_BLOCK_M
+    per_expert = num_tokens * topk / max(num_experts, 1)
+    return PAIR_BLOCK_SIZE_M if per_expert >= PAIR_MIN_PAIRS_PER_EXPERT else BLOCK_SIZE_M
 
 
 def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: int,
@@ -46,15 +59,15 @@ class _Workspace:
         self._cache: Dict[tuple, dict] = {}
 
     def get(self, device: torch.device, num_tokens: int, topk: int, num_experts: int,
-            hidden: int, inter: int) -> dict:
-        key = (device, num_tokens, topk, num_experts, hidden, inter)
+            hidden: int, inter: int, block_m: int) -> dict:
+        key = (device, num_tokens, topk, num_experts, hidden, inter, block_m)
         ws = self._cache.get(key)
         if ws is None:
             if len(self._cache) >= 4:  # bounded: drop the oldest shape
                 self._cache.pop(next(iter(self._cache)))
             pairs = num_tokens * topk
-            capacity = pairs + num_experts * (BLOCK_SIZE_M - 1)
-            blocks = (capacity + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M
+            capacity = pairs + num_experts * (block_m - 1)
+            blocks = (capacity + block_m - 1) // block_m
             i32 = dict(dtype=torch.int32, device=device)
             bf16 = dict(dtype=torch.bfloat16, device=device)
             ws = {
@@ -149,7 +162,8 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
 
     dev = hidden_states.device
     lib = _lib.load()
-    ws = _workspace.get(dev, num_tokens, topk, num_experts, hidden, inter)
+    block_m = choose_block_m(num_tokens, topk, num_experts)
+    ws = _workspace.get(dev, num_tokens, topk, num_experts, hidden, inter, block_m)
     capacity = ws["capacity"]
     gating = gating_output if gating_output.is_contiguous() else gating_output.contiguous()
 
@@ -158,7 +172,7 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
         with _timed("topk_softmax"):
             _C.topk_softmax(ws["topk_weights"], ws["topk_ids"], gating, renormalize=renormalize)
         with _timed("moe_align_block_size"):
-            _C.moe_align_block_size(ws["topk_ids"], num_experts, BLOCK_SIZE_M, ws["sorted_ids"],
+            _C.moe_align_block_size(ws["topk_ids"], num_experts, block_m, ws["sorted_ids"],
                                     ws["expert_ids"], ws["num_post_pad"], fill_pads=True)
         with _timed("gather_rows"):
             _lib.check(lib.b200moe_gather_rows(
@@ -169,13 +183,13 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
             _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
                 ws["a_sorted"].data_ptr(), w1.data_ptr(), ws["act"].data_ptr(),
                 ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity, num_experts,
-                hidden, inter, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
+                hidden, inter, block_m, stream), "grouped_gemm_w13_swiglu")
         with _timed("grouped_gemm_w2_scale"):
             _lib.check(lib.b200moe_grouped_gemm_w2_scale(
                 ws["act"].data_ptr(), w2.data_ptr(), ws["cache3"].data_ptr(),
                 ws["topk_weights"].data_ptr(), ws["sorted_ids"].data_ptr(),
                 ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
-                num_tokens * topk, num_experts, hidden, inter, BLOCK_SIZE_M, stream),
+                num_tokens * topk, num_experts, hidden, inter, block_m, stream),
                 "grouped_gemm_w2_scale")
         _lib.count_launches(3)
         with _timed("moe_sum"):

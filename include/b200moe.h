@@ -198,7 +198,8 @@ int b200moe_scatter_rows(const void* src, void* dst, const int32_t* index, int64
  *   a_sorted  bf16 [sorted_capacity, hidden]   rows in expert-sorted order (b200moe_gather_rows)
  *   w13       bf16 [num_experts, 2*inter, hidden]   gate rows first, then up rows
  *   act       bf16 [sorted_capacity, inter]
- *   block_m   the block_size used for alignment; must be 128
+ *   block_m   the block_size used for alignment: 128 (one CTA per 128 x 256 tile) or 256 (a pair
+ *             of CTAs, tcgen05 cta_group::2, per 256 x 256 tile)
  *   hidden % 64 == 0, inter % 128 == 0 (inter % 64 == 0 when inter < 128 is not supported).
  */
 int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void* w13, void* act,
@@ -216,7 +217,7 @@ int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void* w13, void*
  *
  *   act  bf16 [sorted_capacity, inter], w2 bf16 [num_experts, hidden, inter],
  *   out  bf16 [num_pairs, hidden], topk_weights f32 [num_pairs];
- *   hidden % 128 == 0 (output tile width), inter % 64 == 0, block_m == 128.
+ *   hidden % 256 == 0 (output tile width), inter % 64 == 0, block_m 128 or 256 as above.
  */
 int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, void* out,
                                   const float* topk_weights, const int32_t* sorted_token_ids,

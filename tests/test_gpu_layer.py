@@ -24,21 +24,22 @@ def gemm_status():
     return _lib.load().b200moe_gemm_device_status(1)
 
 
-def aligned(ids_flat, E):
-    s, e, n, _ = moe_oracle.align_ref(ids_flat, BLOCK_SIZE_M, E)
+def aligned(ids_flat, E, block_m=BLOCK_SIZE_M):
+    s, e, n, _ = moe_oracle.align_ref(ids_flat, block_m, E)
     return s, e, n
 
 
 # ------------------------------------------------------------------------------- grouped GEMMs
+@pytest.mark.parametrize("block_m", [128, 256])
 @pytest.mark.parametrize("T,H,I,E", [(100, 256, 128, 8), (300, 512, 1024, 8), (37, 64, 256, 3),
-                                     (1000, 1024, 512, 8), (1, 256, 128, 8)])
-def test_grouped_gemm_w13_swiglu(T, H, I, E):
+                                     (1000, 1024, 512, 8), (1, 256, 128, 8), (3000, 512, 256, 8)])
+def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m):
     lib = _lib.load()
     g = torch.Generator().manual_seed(T + H)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)
     w13 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).to(torch.bfloat16)
     ids = torch.randint(0, E, (T * 2,), generator=g, dtype=torch.int32)
-    s, e, n = aligned(ids.numpy(), E)
+    s, e, n = aligned(ids.numpy(), E, block_m)
     cap, used = s.size, int(n[0])
     rows = torch.from_numpy(s).long().clamp(min=0) // 2
     a_sorted = x[rows].contiguous()
@@ -47,12 +48,12 @@ def test_grouped_gemm_w13_swiglu(T, H, I, E):
     d_a, d_w, d_e, d_n = a_sorted.to(DEV), w13.to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV)
     rc = lib.b200moe_grouped_gemm_w13_swiglu(
         d_a.data_ptr(), d_w.data_ptr(), act.data_ptr(), d_e.data_ptr(), d_n.data_ptr(), cap, E, H, I,
-        BLOCK_SIZE_M, torch.cuda.current_stream().cuda_stream)
+        block_m, torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "w13")
     torch.cuda.synchronize()
     assert gemm_status() == 0
     got = act.cpu().float()
-    slot_expert = torch.from_numpy(np.repeat(e[: used // BLOCK_SIZE_M], BLOCK_SIZE_M)).long()
+    slot_expert = torch.from_numpy(np.repeat(e[: used // block_m], block_m)).long()
     want = torch.zeros(used, I)
     for ex in range(E):
         m = slot_expert == ex
@@ -64,13 +65,14 @@ def test_grouped_gemm_w13_swiglu(T, H, I, E):
     assert (got[used:] == 9.0).all(), "rows beyond num_tokens_post_pad were written"
 
 
+@pytest.mark.parametrize("block_m", [128, 256])
 @pytest.mark.parametrize("T,H,I,E", [(100, 256, 128, 8), (300, 512, 1024, 8), (37, 256, 64, 3),
-                                     (1000, 1024, 512, 8)])
-def test_grouped_gemm_w2_scale(T, H, I, E):
+                                     (1000, 1024, 512, 8), (3000, 512, 256, 8)])
+def test_grouped_gemm_w2_scale(T, H, I, E, block_m):
     lib = _lib.load()
     g = torch.Generator().manual_seed(T + I)
     ids = torch.randint(0, E, (T * 2,), generator=g, dtype=torch.int32)
-    s, e, n = aligned(ids.numpy(), E)
+    s, e, n = aligned(ids.numpy(), E, block_m)
     cap, used = s.size, int(n[0])
     act = torch.randn(cap, I, generator=g).to(torch.bfloat16)
     w2 = (torch.randn(E, H, I, generator=g) / I ** 0.5).to(torch.bfloat16)
@@ -80,7 +82,7 @@ def test_grouped_gemm_w2_scale(T, H, I, E):
     d_s, d_e, d_n = torch.from_numpy(s).to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV)
     rc = lib.b200moe_grouped_gemm_w2_scale(
         d_act.data_ptr(), d_w.data_ptr(), out.data_ptr(), d_tw.data_ptr(), d_s.data_ptr(),
-        d_e.data_ptr(), d_n.data_ptr(), cap, T * 2, E, H, I, BLOCK_SIZE_M,
+        d_e.data_ptr(), d_n.data_ptr(), cap, T * 2, E, H, I, block_m,
         torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "w2")
     torch.cuda.synchronize()
@@ -89,7 +91,7 @@ def test_grouped_gemm_w2_scale(T, H, I, E):
     for slot in range(used):
         p = int(s[slot])
         if p >= 0:
-            ex = int(e[slot // BLOCK_SIZE_M])
+            ex = int(e[slot // block_m])
             want[p] = (act[slot].float() @ w2[ex].float().T) * tw[p]
     st = moe_oracle.error_stats(out.cpu().float(), want)
     assert st["rel_fro"] < 4e-3 and st["max_abs"] < 2e-2 * max(st["ref_max_abs"], 1.0), st
@@ -144,6 +146,24 @@ def test_layer_small_config_in_bf16(golden):
 def test_layer_token_counts(T):
     wl = MoEWorkload("t", T, 512, 256, seed=T)
     check_layer(make_inputs(wl), wl)
+
+
+@pytest.mark.parametrize("T", [5, 700, 4096])
+def test_layer_block_sizes_agree_bit_for_bit(T):
+    """The one-CTA (128-row) and two-CTA (256-row) tilings run the same arithmetic per row."""
+    from electrock_infer_b200.layers.moe import fused_moe as fm
+    wl = MoEWorkload("t", T, 512, 512, seed=100 + T, logit_bias=(1, 0, 0, 0, 0, 0, -1, -3))
+    inp = make_inputs(wl)
+    outs = []
+    try:
+        for bm in (128, 256):
+            fm.FORCE_BLOCK_M = bm
+            outs.append(run_layer(inp, wl)[1].clone())
+    finally:
+        fm.FORCE_BLOCK_M = None
+    assert torch.equal(outs[0], outs[1])
+    assert fm.choose_block_m(8192, 2, 8) == 256 and fm.choose_block_m(256, 2, 8) == 128
+    check_layer(inp, wl)
 
 
 def test_layer_skewed_and_empty_experts():
