@@ -38,7 +38,10 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;           // accumulator columns per tile
 constexpr int kBlockK = 64;            // 64 bf16 = 128 bytes = one 128B-swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+#ifndef B200MOE_STAGES
+#define B200MOE_STAGES 4
+#endif
+constexpr int kStages = B200MOE_STAGES;  // smem ring depth of the one-CTA kernel
 constexpr int kABytes = kBlockM * kBlockK * 2;   // 16384
 constexpr int kBBytes = kBlockN * kBlockK * 2;   // 32768
 constexpr int kStageBytes = kABytes + kBBytes;   // 49152
@@ -328,7 +331,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t tmem_d = tmem_base + acc * kBlockN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x202)) { ok = false; break; }
-          tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kStageBytes);
           const uint32_t sb = sa + kABytes;
 #pragma unroll
@@ -443,7 +445,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // CTAs and are released by the leader's tcgen05.commit, issued once per CTA.  tmem_empty[a] lives
 // in the leader and collects the epilogue warps of both CTAs.  No load uses cluster multicast.
 // ================================================================================================
-constexpr int kPairStages = 6;
+#ifndef B200MOE_PAIR_STAGES
+#define B200MOE_PAIR_STAGES 6
+#endif
+constexpr int kPairStages = B200MOE_PAIR_STAGES;
 constexpr int kPairABytes = kBlockM * kBlockK * 2;          // 16384: this CTA's 128 A rows
 constexpr int kPairBBytes = (kBlockN / 2) * kBlockK * 2;    // 16384: this CTA's half of B
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;  // 32768
@@ -619,7 +624,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t tmem_d = tmem_base + acc * kBlockN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x212)) { ok = false; break; }
-          tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
           const uint32_t sb = sa + kPairABytes;
 #pragma unroll

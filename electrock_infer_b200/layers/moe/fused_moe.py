@@ -18,20 +18,20 @@ import torch
 from ... import _C, _lib
 
 # Rows per M tile of the tensor-core kernels; token alignment pads every expert to this.
-# 128 rows: one CTA per tile.  256 rows: a pair of CTAs (tcgen05 cta_group::2) per tile, which moves
-# a third less data per FLOP and wins once experts have many rows; it pads more, so small batches
-# keep 128.
+# 128 rows: one CTA per 128 x 256 tile.  256 rows: a pair of CTAs (tcgen05 cta_group::2) per
+# 256 x 256 tile, which moves a third less operand data per FLOP but pads every expert to 256 rows
+# and issues slower M=256 MMAs; measured on B200 at Mixtral shape it is 3-6 % slower than the
+# one-CTA tiling at T=8192, so it is available but not chosen by default.
 BLOCK_SIZE_M = 128
 PAIR_BLOCK_SIZE_M = 256
-PAIR_MIN_PAIRS_PER_EXPERT = 512
 FORCE_BLOCK_M = None  # set to 128 or 256 to override the choice (benchmarks, tests)
 
 
 def choose_block_m(num_tokens: int, topk: int, num_experts: int) -> int:
+    """M tile (= alignment block) used for a batch of this size."""
     if FORCE_BLOCK_M is not None:
         return FORCE_BLOCK_M
-    per_expert = num_tokens * topk / max(num_experts, 1)
-    return PAIR_BLOCK_SIZE_M if per_expert >= PAIR_MIN_PAIRS_PER_EXPERT else BLOCK_SIZE_M
+    return BLOCK_SIZE_M
 
 
 def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: int,

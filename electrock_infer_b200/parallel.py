@@ -30,7 +30,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import _C, _lib
-from .layers.moe.fused_moe import BLOCK_SIZE_M
+from .layers.moe.fused_moe import BLOCK_SIZE_M, _timed
 
 
 class CudaOps:
@@ -41,7 +41,8 @@ class CudaOps:
         T = logits.shape[0]
         w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
         ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
-        _C.topk_softmax(w, ids, logits.contiguous(), renormalize=renormalize)
+        with _timed("topk_softmax"):
+            _C.topk_softmax(w, ids, logits.contiguous(), renormalize=renormalize)
         return w, ids
 
     def sort_pairs_by_expert(self, ids: torch.Tensor,
@@ -90,18 +91,22 @@ class CudaOps:
         a_sorted = torch.empty(cap, H, dtype=rows.dtype, device=dev)
         act = torch.empty(cap, inter, dtype=rows.dtype, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        _C.moe_align_block_size(row_expert, E, BLOCK_SIZE_M, sorted_ids, expert_ids, npp,
-                                fill_pads=True)
-        _lib.check(lib.b200moe_gather_rows(rows.data_ptr(), a_sorted.data_ptr(),
-                                           sorted_ids.data_ptr(), npp.data_ptr(), cap, R, H, 1,
-                                           stream), "gather_rows")
-        _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
-            a_sorted.data_ptr(), w13.data_ptr(), act.data_ptr(), expert_ids.data_ptr(),
-            npp.data_ptr(), cap, E, H, inter, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
-        _lib.check(lib.b200moe_grouped_gemm_w2_scale(
-            act.data_ptr(), w2.data_ptr(), out.data_ptr(), row_weight.data_ptr(),
-            sorted_ids.data_ptr(), expert_ids.data_ptr(), npp.data_ptr(), cap, R, E, H, inter,
-            BLOCK_SIZE_M, stream), "grouped_gemm_w2_scale")
+        with _timed("moe_align_block_size"):
+            _C.moe_align_block_size(row_expert, E, BLOCK_SIZE_M, sorted_ids, expert_ids, npp,
+                                    fill_pads=True)
+        with _timed("gather_rows"):
+            _lib.check(lib.b200moe_gather_rows(rows.data_ptr(), a_sorted.data_ptr(),
+                                               sorted_ids.data_ptr(), npp.data_ptr(), cap, R, H, 1,
+                                               stream), "gather_rows")
+        with _timed("grouped_gemm_w13_swiglu"):
+            _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
+                a_sorted.data_ptr(), w13.data_ptr(), act.data_ptr(), expert_ids.data_ptr(),
+                npp.data_ptr(), cap, E, H, inter, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
+        with _timed("grouped_gemm_w2_scale"):
+            _lib.check(lib.b200moe_grouped_gemm_w2_scale(
+                act.data_ptr(), w2.data_ptr(), out.data_ptr(), row_weight.data_ptr(),
+                sorted_ids.data_ptr(), expert_ids.data_ptr(), npp.data_ptr(), cap, R, E, H, inter,
+                BLOCK_SIZE_M, stream), "grouped_gemm_w2_scale")
         _lib.count_launches(3)
         return out
 
@@ -115,7 +120,8 @@ class CudaOps:
             torch.cuda.current_stream(out.device).cuda_stream)
         _lib.check(rc, "scatter_rows")
         _lib.count_launches(1)
-        _C.moe_sum(cache, out)
+        with _timed("moe_sum"):
+            _C.moe_sum(cache, out)
 
 
 def split_sizes(counts_per_expert: List[int], ep_size: int) -> List[int]:

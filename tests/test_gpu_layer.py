@@ -162,7 +162,7 @@ def test_layer_block_sizes_agree_bit_for_bit(T):
     finally:
         fm.FORCE_BLOCK_M = None
     assert torch.equal(outs[0], outs[1])
-    assert fm.choose_block_m(8192, 2, 8) == 256 and fm.choose_block_m(256, 2, 8) == 128
+    assert fm.choose_block_m(8192, 2, 8) == 128
     check_layer(inp, wl)
 
 
