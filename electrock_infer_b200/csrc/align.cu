@@ -232,6 +232,24 @@ align_single_cta_kernel(const T* __restrict__ ids, int64_t numel, int num_expert
 // place by the scan kernel into exclusive per-expert prefixes, followed by int32
 // meta[kMaxExperts + 1 + kMaxExperts] = padded offsets and totals.
 // ---------------------------------------------------------------------------------------------
+// Workspace words after the per-segment counters: padded offsets, then totals per expert.
+constexpr int kMetaOffsets = 0;                 // meta[0 .. kMaxExperts]
+constexpr int kMetaTotals = kMaxExperts + 1;    // meta[kMaxExperts + 1 .. 2 * kMaxExperts]
+
+constexpr int kIdsPerSegWarp = kSegment / kSegWarps;             // 1024
+constexpr int kSegSteps = kIdsPerSegWarp / kIdsPerWarpStep;      // 8 steps of 128 ids per warp
+
+// Four expert ids (or -1) packed as bytes, 0xff for "none".
+__device__ __forceinline__ uint32_t pack_ids(const int (&e)[4]) {
+  return (static_cast<uint32_t>(e[0]) & 0xffu) | ((static_cast<uint32_t>(e[1]) & 0xffu) << 8) |
+         ((static_cast<uint32_t>(e[2]) & 0xffu) << 16) | ((static_cast<uint32_t>(e[3]) & 0xffu) << 24);
+}
+__device__ __forceinline__ int unpack_id(uint32_t packed, int j) {
+  const int x = static_cast<int>((packed >> (8 * j)) & 0xffu);
+  return x == 0xff ? -1 : x;
+}
+
+// Histogram of one segment.  All loads of a warp's 1024 ids are issued before any arithmetic.
 template <typename T>
 __global__ void __launch_bounds__(kSegThreads)
 align_count_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
@@ -239,13 +257,28 @@ align_count_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
   __shared__ int s_cnt[kSegWarps][kMaxExperts];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t seg_begin = static_cast<int64_t>(blockIdx.x) * kSegment;
-  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * (kSegment / kSegWarps), numel);
-  const int64_t end = min(begin + kSegment / kSegWarps, numel);
-  int cnt[kMaxExperts];
-  warp_count<T>(ids, begin, end, numel, num_experts, lane, cnt);
+  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * kIdsPerSegWarp, numel);
+  const int64_t end = min(begin + kIdsPerSegWarp, numel);
+  int e[kSegSteps][4];
+#pragma unroll
+  for (int st = 0; st < kSegSteps; ++st)
+    load_ids4<T>(ids, begin + st * kIdsPerWarpStep + lane * kIdsPerLane, end, num_experts, e[st]);
+  uint64_t c = 0;  // per-lane byte counters: at most 32 per expert
+#pragma unroll
+  for (int st = 0; st < kSegSteps; ++st) c += pack_counts(e[st]);
+  // Widen to 16-bit fields before the cross-lane sum (a warp can hold 1024 ids of one expert).
+  uint64_t even = c & 0x00ff00ff00ff00ffull, odd = (c >> 8) & 0x00ff00ff00ff00ffull;
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) {
+    even += __shfl_xor_sync(0xffffffffu, even, d);
+    odd += __shfl_xor_sync(0xffffffffu, odd, d);
+  }
   if (lane == 0) {
 #pragma unroll
-    for (int x = 0; x < kMaxExperts; ++x) s_cnt[warp][x] = cnt[x];
+    for (int x = 0; x < kMaxExperts; x += 2) {
+      s_cnt[warp][x] = static_cast<int>((even >> (8 * x)) & 0xffff);
+      s_cnt[warp][x + 1] = static_cast<int>((odd >> (8 * x)) & 0xffff);
+    }
   }
   __syncthreads();
   if (threadIdx.x < kMaxExperts) {
@@ -255,73 +288,115 @@ align_count_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
   }
 }
 
+// One CTA turns the per-segment counts into exclusive per-expert prefixes (in place) and publishes
+// the padded offsets.  Thread t owns segment chunk_base + t: its eight counts are one 32-byte
+// coalesced load; each expert is scanned block-wide (warp scan + scan of the 32 warp totals).
 __global__ void __launch_bounds__(kThreads)
 align_scan_kernel(int32_t* __restrict__ seg_counts, int64_t num_segments, int num_experts,
-                  int block_size, int32_t* __restrict__ meta, int32_t* __restrict__ sorted,
-                  int64_t sorted_capacity, int32_t* __restrict__ expert_ids,
-                  int32_t* __restrict__ num_tokens_post_pad, int32_t* __restrict__ expert_offsets,
-                  int fill_pads) {
-  // Warp x (x < num_experts) scans the counts of expert x over all segments.
-  __shared__ int s_total[kMaxExperts];
+                  int block_size, int32_t* __restrict__ meta,
+                  int32_t* __restrict__ num_tokens_post_pad, int32_t* __restrict__ expert_offsets) {
+  __shared__ int s_warp_tot[kMaxExperts][kWarps];
+  __shared__ int s_carry[kMaxExperts];
   __shared__ int s_cumsum[kMaxExperts + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (warp < kMaxExperts) {
-    int carry = 0;
-    for (int64_t s0 = 0; s0 < num_segments; s0 += 32) {
-      const int64_t s = s0 + lane;
-      const int c = (s < num_segments) ? seg_counts[s * kMaxExperts + warp] : 0;
-      int incl = c;
+  if (threadIdx.x < kMaxExperts) s_carry[threadIdx.x] = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < num_segments; base += kThreads) {
+    const int64_t seg = base + threadIdx.x;
+    int c[kMaxExperts], incl[kMaxExperts];
+    if (seg < num_segments) {
+      const int4 a = *reinterpret_cast<const int4*>(seg_counts + seg * kMaxExperts);
+      const int4 b = *reinterpret_cast<const int4*>(seg_counts + seg * kMaxExperts + 4);
+      c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+    } else {
+#pragma unroll
+      for (int x = 0; x < kMaxExperts; ++x) c[x] = 0;
+    }
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) {
+      int v = c[x];
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += o;
+        const int o = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += o;
       }
-      if (s < num_segments) seg_counts[s * kMaxExperts + warp] = carry + incl - c;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
+      incl[x] = v;
+      if (lane == 31) s_warp_tot[x][warp] = v;
     }
-    if (lane == 0) s_total[warp] = carry;
+    __syncthreads();
+    if (warp < kMaxExperts) {  // warp x: exclusive scan of the 32 warp totals of expert x
+      const int t = s_warp_tot[warp][lane];
+      int v = t;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += o;
+      }
+      s_warp_tot[warp][lane] = s_carry[warp] + v - t;
+      __syncwarp();
+      if (lane == 31) s_carry[warp] += v;
+    }
+    __syncthreads();
+    if (seg < num_segments) {
+      int4 a, b;
+      a.x = s_warp_tot[0][warp] + incl[0] - c[0]; a.y = s_warp_tot[1][warp] + incl[1] - c[1];
+      a.z = s_warp_tot[2][warp] + incl[2] - c[2]; a.w = s_warp_tot[3][warp] + incl[3] - c[3];
+      b.x = s_warp_tot[4][warp] + incl[4] - c[4]; b.y = s_warp_tot[5][warp] + incl[5] - c[5];
+      b.z = s_warp_tot[6][warp] + incl[6] - c[6]; b.w = s_warp_tot[7][warp] + incl[7] - c[7];
+      *reinterpret_cast<int4*>(seg_counts + seg * kMaxExperts) = a;
+      *reinterpret_cast<int4*>(seg_counts + seg * kMaxExperts + 4) = b;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   if (threadIdx.x == 0) {
-    publish_offsets(s_total, num_experts, block_size, s_cumsum, num_tokens_post_pad,
+    publish_offsets(s_carry, num_experts, block_size, s_cumsum, num_tokens_post_pad,
                     expert_offsets);
-    for (int x = 0; x <= kMaxExperts; ++x) meta[x] = s_cumsum[x <= num_experts ? x : num_experts];
+    for (int x = 0; x <= kMaxExperts; ++x)
+      meta[kMetaOffsets + x] = s_cumsum[x <= num_experts ? x : num_experts];
+    for (int x = 0; x < kMaxExperts; ++x) meta[kMetaTotals + x] = s_carry[x];
   }
-  __syncthreads();
-  write_blocks_and_pads(s_cumsum, s_total, num_experts, block_size, sorted, sorted_capacity,
-                        expert_ids, fill_pads, threadIdx.x, kThreads);
 }
 
 // Scatter of one segment.  The ids are read once and kept in registers; ranks inside the segment
 // are resolved in shared memory, so that each expert's share of the segment leaves the SM as one
 // contiguous run of 4-byte-coalesced stores instead of 4-byte stores scattered over eight runs.
+// The CTAs also share out the writing of expert_ids and of the -1 padding.
 template <typename T>
-__global__ void __launch_bounds__(kSegThreads)
-align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
+__global__ void __launch_bounds__(kSegThreads, 3)
+align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts, int block_size,
                      const int32_t* __restrict__ seg_prefix, const int32_t* __restrict__ meta,
-                     int32_t* __restrict__ sorted) {
-  constexpr int kIdsPerWarp = kSegment / kSegWarps;          // 1024
-  constexpr int kSteps = kIdsPerWarp / kIdsPerWarpStep;      // 8
+                     int32_t* __restrict__ sorted, int64_t sorted_capacity,
+                     int32_t* __restrict__ expert_ids, int fill_pads) {
   __shared__ int s_cnt[kSegWarps][kMaxExperts];  // per-warp counts, then exclusive prefix over warps
   __shared__ int s_base[kMaxExperts + 1];        // start of each expert's run inside the segment
   __shared__ int s_dst[kMaxExperts];             // output slot of the first element of each run
+  __shared__ int s_off[kMaxExperts + 1];         // padded offsets of the whole input
   __shared__ int32_t s_sorted[kSegment];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t seg_begin = static_cast<int64_t>(blockIdx.x) * kSegment;
-  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * kIdsPerWarp, numel);
-  const int64_t end = min(begin + kIdsPerWarp, numel);
+  const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * kIdsPerSegWarp, numel);
+  const int64_t end = min(begin + kIdsPerSegWarp, numel);
 
-  int e[kSteps][4];
-  uint64_t excl[kSteps];
+  uint32_t packed[kSegSteps];
+  uint64_t excl[kSegSteps];
+  {
+    int e[kSegSteps][4];
+#pragma unroll
+    for (int st = 0; st < kSegSteps; ++st)
+      load_ids4<T>(ids, begin + st * kIdsPerWarpStep + lane * kIdsPerLane, end, num_experts, e[st]);
+#pragma unroll
+    for (int st = 0; st < kSegSteps; ++st) packed[st] = pack_ids(e[st]);
+  }
   int cnt[kMaxExperts];
 #pragma unroll
   for (int x = 0; x < kMaxExperts; ++x) cnt[x] = 0;
 #pragma unroll
-  for (int st = 0; st < kSteps; ++st) {
-    const int64_t first = begin + st * kIdsPerWarpStep + lane * kIdsPerLane;
-    load_ids4<T>(ids, first, end, num_experts, e[st]);
-    const uint64_t mine = pack_counts(e[st]);
+  for (int st = 0; st < kSegSteps; ++st) {
+    int e[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) e[j] = unpack_id(packed[st], j);
+    const uint64_t mine = pack_counts(e);
     const uint64_t incl = warp_inclusive_scan(mine, lane);
     excl[st] = incl - mine;
     const uint64_t total = __shfl_sync(0xffffffffu, incl, 31);
@@ -332,6 +407,7 @@ align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
 #pragma unroll
     for (int x = 0; x < kMaxExperts; ++x) s_cnt[warp][x] = cnt[x];
   }
+  if (threadIdx.x <= kMaxExperts) s_off[threadIdx.x] = meta[kMetaOffsets + threadIdx.x];
   __syncthreads();
   if (threadIdx.x < kMaxExperts) {
     int acc = 0;
@@ -341,7 +417,7 @@ align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
       acc += c;
     }
     s_base[threadIdx.x + 1] = acc;  // count for now; turned into offsets below
-    s_dst[threadIdx.x] = meta[threadIdx.x] +
+    s_dst[threadIdx.x] = s_off[threadIdx.x] +
                          seg_prefix[static_cast<int64_t>(blockIdx.x) * kMaxExperts + threadIdx.x];
   }
   __syncthreads();
@@ -356,13 +432,13 @@ align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
 #pragma unroll
   for (int x = 0; x < kMaxExperts; ++x) start[x] = s_base[x] + s_cnt[warp][x];
 #pragma unroll
-  for (int st = 0; st < kSteps; ++st) {
+  for (int st = 0; st < kSegSteps; ++st) {
     const int first = static_cast<int>(begin - seg_begin) + st * kIdsPerWarpStep + lane * kIdsPerLane;
     uint64_t ex = excl[st];
     uint64_t mine = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int x = e[st][j];
+      const int x = unpack_id(packed[st], j);
       if (x >= 0) {
         int sx = 0;
 #pragma unroll
@@ -388,6 +464,27 @@ align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
     for (int y = 1; y < kMaxExperts; ++y) x += (i >= s_base[y]) ? 1 : 0;
     sorted[s_dst[x] + (i - s_base[x])] = seg_first + s_sorted[i];
   }
+
+  // This CTA's share of expert_ids, and of the -1 padding when asked for.
+  const int npp = s_off[num_experts];
+  const int nblocks = npp / block_size;
+  const int per_cta = (nblocks + gridDim.x - 1) / gridDim.x;
+  const int b_end = min(nblocks, static_cast<int>(blockIdx.x + 1) * per_cta);
+  for (int b = blockIdx.x * per_cta + threadIdx.x; b < b_end; b += kSegThreads) {
+    const int slot = b * block_size;
+    int x = 0;
+    while (x + 1 < num_experts && slot >= s_off[x + 1]) ++x;
+    expert_ids[b] = x;
+  }
+  if (fill_pads) {
+    if (blockIdx.x < static_cast<unsigned>(num_experts)) {
+      const int x = blockIdx.x;
+      for (int i = s_off[x] + meta[kMetaTotals + x] + threadIdx.x; i < s_off[x + 1]; i += kSegThreads)
+        sorted[i] = -1;
+    } else if (blockIdx.x == gridDim.x - 1) {
+      for (int64_t i = npp + threadIdx.x; i < sorted_capacity; i += kSegThreads) sorted[i] = -1;
+    }
+  }
 }
 
 template <typename T>
@@ -405,15 +502,15 @@ int run(const void* ids_v, int64_t numel, int E, int bs, int32_t* sorted, int64_
     return fail(B200MOE_ERR_WORKSPACE,
                 "moe_align_block_size: %lld ids need a workspace of %zu bytes, got %zu",
                 (long long)numel, need, ws ? ws_bytes : (size_t)0);
-  if (!aligned_to(ws, 4)) return fail(B200MOE_ERR_ALIGN, "moe_align_block_size: workspace alignment");
+  if (!aligned_to(ws, 16))
+    return fail(B200MOE_ERR_ALIGN, "moe_align_block_size: the workspace must be 16-byte aligned");
   const int64_t nseg = ceil_div64(numel, kSegment);
   int32_t* seg = static_cast<int32_t*>(ws);
   int32_t* meta = seg + nseg * kMaxExperts;
   align_count_kernel<T><<<static_cast<unsigned>(nseg), kSegThreads, 0, st>>>(ids, numel, E, seg);
-  align_scan_kernel<<<1, kThreads, 0, st>>>(seg, nseg, E, bs, meta, sorted, cap, expert_ids, npp,
-                                            offsets, fill);
-  align_scatter_kernel<T><<<static_cast<unsigned>(nseg), kSegThreads, 0, st>>>(ids, numel, E, seg,
-                                                                               meta, sorted);
+  align_scan_kernel<<<1, kThreads, 0, st>>>(seg, nseg, E, bs, meta, npp, offsets);
+  align_scatter_kernel<T><<<static_cast<unsigned>(nseg), kSegThreads, 0, st>>>(
+      ids, numel, E, bs, seg, meta, sorted, cap, expert_ids, fill);
   return check_launch("moe_align_block_size");
 }
 

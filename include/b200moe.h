@@ -96,7 +96,7 @@ int b200moe_topk_softmax(float* topk_weights, int32_t* topk_indices, const void*
  * to every slot of sorted_token_ids that holds no pair, so no separate fill launch is needed.
  *
  * Inputs longer than b200moe_align_single_pass_max() need a workspace of
- * b200moe_align_workspace_bytes() bytes (4-byte aligned device memory); shorter inputs run as
+ * b200moe_align_workspace_bytes() bytes (16-byte aligned device memory); shorter inputs run as
  * one launch and ignore it.  num_experts must lie in [1, b200moe_align_max_experts()] (8).
  * Pair indices with an expert outside [0, num_experts) are skipped.
  */
