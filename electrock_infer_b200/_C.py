@@ -70,14 +70,17 @@ def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: i
                          sorted_token_ids: torch.Tensor, expert_ids: torch.Tensor,
                          num_tokens_post_pad: torch.Tensor,
                          expert_offsets: torch.Tensor | None = None,
-                         fill_pads: bool = False) -> None:
+                         fill_pads: bool = False,
+                         workspace: torch.Tensor | None = None) -> None:
     """Stable counting sort of pair indices by expert with per-expert padding
     (src/moe_align_block_size.cu:140-230).
 
     With the defaults the op writes exactly what the reference kernel writes (padding slots and
     the tail are left as the caller prefilled them).  ``fill_pads=True`` makes the kernel write the
     ``-1`` padding itself; ``expert_offsets`` (i32 ``[num_experts + 1]``) optionally receives the
-    padded start offset of every expert.  Both are extensions.
+    padded start offset of every expert.  Both are extensions.  Long inputs need a small scratch
+    tensor (``align_workspace_numel`` int32 elements); it is allocated here unless ``workspace``
+    is passed.
     """
     name = "moe_align_block_size"
     outs = [sorted_token_ids, expert_ids, num_tokens_post_pad]
@@ -97,8 +100,17 @@ def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: i
     numel = topk_ids.numel()
     ws_bytes = lib.b200moe_align_workspace_bytes(numel, num_experts)
     ws = None
+    own_ws = False
     if ws_bytes:
-        ws = torch.empty(ws_bytes // 4, dtype=torch.int32, device=dev)
+        if workspace is not None:
+            if (workspace.dtype != torch.int32 or workspace.device != dev
+                    or workspace.numel() * 4 < ws_bytes):
+                raise RuntimeError(f"{name}: workspace must be an int32 tensor of at least "
+                                   f"{ws_bytes // 4} elements on {dev}")
+            ws = workspace
+        else:
+            ws = torch.empty(ws_bytes // 4, dtype=torch.int32, device=dev)
+            own_ws = True
     with torch.cuda.device(dev):
         rc = lib.b200moe_align_block_size(
             topk_ids.data_ptr(), _INT_TAGS[topk_ids.dtype], numel, int(num_experts),
@@ -108,8 +120,14 @@ def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: i
             ws.data_ptr() if ws is not None else None, ws_bytes, _stream(dev))
     _lib.check(rc, name)
     _lib.count_launches(3 if ws is not None else 1)
-    if ws is not None:
+    if own_ws:
         ws.record_stream(torch.cuda.current_stream(dev))
+
+
+def align_workspace_numel(numel: int, num_experts: int) -> int:
+    """int32 elements of scratch that ``moe_align_block_size`` needs for ``numel`` pair indices
+    (0 for short inputs)."""
+    return _lib.load().b200moe_align_workspace_bytes(numel, num_experts) // 4
 
 
 def silu_and_mul(out: torch.Tensor, input: torch.Tensor) -> None:  # noqa: A002 - reference name

@@ -9,10 +9,9 @@
 // The reference runs one CTA of one warp.  Here a warp ranks 128 consecutive ids per step: every
 // lane loads four ids with one 16-byte load, keeps eight per-expert counters packed as bytes of a
 // 64-bit word, and one packed warp prefix scan yields the stable rank of all 128 ids at once.
-// Inputs up to kSinglePassMax ids run as one CTA in one launch (the layer's case: a few thousand
-// to a few tens of thousands of ids).  Longer inputs use three launches over segments of
-// kSegment ids: per-segment histogram, a one-CTA scan over segments, and a scatter that re-reads
-// the ids (from L2 at these sizes).
+// Inputs up to kSinglePassMax ids run as one CTA in one launch (decode-sized batches).  Longer
+// inputs use three launches over segments of kSegment ids: per-segment histogram, a one-CTA scan
+// over segments, and a scatter that re-reads the ids (from L2 at these sizes).
 #include <mutex>
 
 #include "common.cuh"
@@ -25,7 +24,7 @@ constexpr int kIdsPerLane = 4;
 constexpr int kIdsPerWarpStep = 32 * kIdsPerLane;  // 128: a per-expert count fits in a byte
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
-constexpr int64_t kSinglePassMax = 65536;
+constexpr int64_t kSinglePassMax = 8192;
 
 constexpr int kSegThreads = 256;
 constexpr int kSegWarps = kSegThreads / 32;
@@ -477,13 +476,11 @@ align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts, 
     expert_ids[b] = x;
   }
   if (fill_pads) {
-    if (blockIdx.x < static_cast<unsigned>(num_experts)) {
-      const int x = blockIdx.x;
+    for (int x = blockIdx.x; x < num_experts; x += gridDim.x)
       for (int i = s_off[x] + meta[kMetaTotals + x] + threadIdx.x; i < s_off[x + 1]; i += kSegThreads)
         sorted[i] = -1;
-    } else if (blockIdx.x == gridDim.x - 1) {
+    if (blockIdx.x == gridDim.x - 1)
       for (int64_t i = npp + threadIdx.x; i < sorted_capacity; i += kSegThreads) sorted[i] = -1;
-    }
   }
 }
 

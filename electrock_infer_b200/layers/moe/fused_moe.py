@@ -77,6 +77,7 @@ class _Workspace:
                 "sorted_ids": torch.empty(capacity, **i32),
                 "expert_ids": torch.zeros(blocks, **i32),
                 "num_post_pad": torch.zeros(1, **i32),
+                "align_ws": torch.empty(max(_C.align_workspace_numel(pairs, num_experts), 1), **i32),
                 "a_sorted": torch.empty(capacity, hidden, **bf16),
                 "act": torch.empty(capacity, inter, **bf16),
                 "cache3": torch.empty(num_tokens, topk, hidden, **bf16),
@@ -173,7 +174,8 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
             _C.topk_softmax(ws["topk_weights"], ws["topk_ids"], gating, renormalize=renormalize)
         with _timed("moe_align_block_size"):
             _C.moe_align_block_size(ws["topk_ids"], num_experts, block_m, ws["sorted_ids"],
-                                    ws["expert_ids"], ws["num_post_pad"], fill_pads=True)
+                                    ws["expert_ids"], ws["num_post_pad"], fill_pads=True,
+                                    workspace=ws["align_ws"])
         with _timed("gather_rows"):
             _lib.check(lib.b200moe_gather_rows(
                 hidden_states.data_ptr(), ws["a_sorted"].data_ptr(), ws["sorted_ids"].data_ptr(),

@@ -95,7 +95,7 @@ int b200moe_topk_softmax(float* topk_weights, int32_t* topk_indices, const void*
  * (layers/moe/moe_align_block_size.py:39-42).  With fill_pads != 0 the kernel itself writes -1
  * to every slot of sorted_token_ids that holds no pair, so no separate fill launch is needed.
  *
- * Inputs longer than b200moe_align_single_pass_max() need a workspace of
+ * Inputs longer than b200moe_align_single_pass_max() (8192) need a workspace of
  * b200moe_align_workspace_bytes() bytes (16-byte aligned device memory); shorter inputs run as
  * one launch and ignore it.  num_experts must lie in [1, b200moe_align_max_experts()] (8).
  * Pair indices with an expert outside [0, num_experts) are skipped.

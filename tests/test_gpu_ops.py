@@ -111,8 +111,8 @@ def test_align_golden(golden, case, bs):
     assert (s[npp:] == -1).all()                                    # tail untouched (prefill)
 
 
-@pytest.mark.parametrize("numel", [0, 1, 2, 127, 128, 129, 4097, 32768, 65535, 65536, 65537,
-                                   70000, 131072, 1000003])
+@pytest.mark.parametrize("numel", [0, 1, 2, 127, 128, 129, 4097, 8191, 8192, 8193, 8300, 16384,
+                                   32768, 65535, 65536, 65537, 70000, 131072, 1000003])
 @pytest.mark.parametrize("fill", [False, True])
 def test_align_sizes(numel, fill):
     rng = np.random.default_rng(numel + 1)
