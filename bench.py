@@ -207,6 +207,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=dev)
     if world > 1 and args.parallel == "ep":
         from electrock_infer_b200.parallel import ExpertParallelMoE
