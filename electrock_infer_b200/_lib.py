@@ -41,6 +41,9 @@ SIGNATURES = {
     "b200moe_grouped_gemm_w13_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_int64, c_int, c_int64, c_int64, c_int,
                                                 c_void_p]),
+    "b200moe_grouped_gemm_w13_swiglu_gather": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                                       c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                                       c_int64, c_int64, c_int, c_void_p]),
     "b200moe_grouped_gemm_w2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
                                               c_int64, c_int, c_void_p]),

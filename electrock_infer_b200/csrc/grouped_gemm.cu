@@ -54,7 +54,8 @@ constexpr long long kWaitCycles = 1ll << 31;
 constexpr int kSmemAlignSlack = 1024;
 constexpr int kSmemBytes = kStages * kStageBytes + kSmemAlignSlack;
 
-enum Mode { kW13 = 0, kW2 = 1 };
+// kW13Gather is kW13 with the A rows fetched straight from the token tensor by TMA row gathers.
+enum Mode { kW13 = 0, kW2 = 1, kW13Gather = 2 };
 
 // Device status word: 0 = fine; otherwise (role << 8) | barrier kind of the wait that ran out.
 __device__ int g_gemm_status = 0;
@@ -116,6 +117,18 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0),
       "r"(c1)
+      : "memory");
+}
+// Four rows of a 2-D tensor (box = 64 columns x 1 row) gathered into four consecutive 128-byte
+// rows of shared memory; the 128-byte swizzle is a function of the destination address, so 32
+// such gathers lay out a 128-row tile exactly like one tiled box.
+__device__ __forceinline__ void tma_gather4(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int col, int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(col),
+      "r"(r0), "r"(r1), "r"(r2), "r"(r3)
       : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
@@ -225,6 +238,8 @@ struct GemmParams {
   int b_rows_per_expert;         // kW13: 2 * inter; kW2: hidden
   int inter;                     // kW13: offset of the up rows inside an expert's w13
   long long out_ld;              // leading dimension of out in elements
+  int top_k;                     // kW13Gather: A row of slot s is sorted[s] / top_k
+  int num_src_rows;              // kW13Gather: rows of the token tensor
 };
 
 template <int kMode>
@@ -287,7 +302,49 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const long long total_tiles = static_cast<long long>(s_blk_off[p.num_experts]) * p.n_tiles;
   volatile int* abort_flag = &s_abort;
 
-  if (warp == 0) {
+  constexpr bool kIsW13 = (kMode != kW2);
+  if (warp == 0 && kMode == kW13Gather) {
+    // ---------------------------------------------------------------- TMA producer, gathered A
+    // Lane l owns slots 4l .. 4l+3 of the M block and issues one row gather per K step; lane 0
+    // also owns the barrier bookkeeping and the weight loads.
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
+      const int b_row0 = c.expert * p.b_rows_per_expert + c.n_tile * (kBlockN / 2);
+      int rows[4];
+      {
+        const int4 ids = *reinterpret_cast<const int4*>(
+            p.sorted + static_cast<long long>(c.m_block) * kBlockM + lane * 4);
+        const int raw[4] = {ids.x, ids.y, ids.z, ids.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = raw[j] >= 0 ? raw[j] / p.top_k : 0;  // padding slots read row 0: unused
+          rows[j] = r < p.num_src_rows ? r : 0;
+        }
+      }
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        int good = 1;
+        if (lane == 0) {
+          good = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x101) ? 1 : 0;
+          if (good) mbar_expect_tx(&full_bar[stage], kStageBytes);
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { ok = false; break; }
+        uint8_t* sa = smem + stage * kStageBytes;
+        tma_gather4(sa + lane * 512, &tmap_a, &full_bar[stage], kb * kBlockK, rows[0], rows[1],
+                    rows[2], rows[3]);
+        if (lane == 0) {
+          uint8_t* sb = sa + kABytes;
+          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
+          tma_load_2d(sb + kBBytes / 2, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0 + p.inter);
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       int stage = 0;
@@ -297,14 +354,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
         const int a_row = c.m_block * kBlockM;
         const int b_row0 = c.expert * p.b_rows_per_expert +
-                           c.n_tile * (kMode == kW13 ? kBlockN / 2 : kBlockN);
+                           c.n_tile * (kIsW13 ? kBlockN / 2 : kBlockN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x101)) { ok = false; break; }
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
           mbar_expect_tx(&full_bar[stage], kStageBytes);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBlockK, a_row);
-          if (kMode == kW13) {
+          if (kIsW13) {
             tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
             tma_load_2d(sb + kBBytes / 2, &tmap_b, &full_bar[stage], kb * kBlockK,
                         b_row0 + p.inter);
@@ -364,7 +421,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * kBlockN);
-      if (kMode == kW13) {
+      if (kIsW13) {
         __nv_bfloat16* dst = p.out + slot * p.out_ld + static_cast<long long>(c.n_tile) * (kBlockN / 2);
 #pragma unroll 1
         for (int ch = 0; ch < (kBlockN / 2) / 32; ++ch) {
@@ -845,6 +902,51 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   p.out_ld = inter;
   if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_grouped_gemm_w13_swiglu_gather(
+    const void* tokens, int64_t num_tokens, int top_k, const int32_t* sorted_token_ids,
+    const void* w13, void* act, const int32_t* expert_ids, const int32_t* num_tokens_post_pad,
+    int64_t sorted_capacity, int num_experts, int64_t hidden, int64_t inter, int block_m,
+    b200moe_stream_t stream) {
+  using namespace b200moe;
+  const char* name = "grouped_gemm_w13_swiglu_gather";
+  if (int rc = check_common(name, num_experts, hidden, inter, block_m, sorted_capacity)) return rc;
+  if (block_m != kBlockM)
+    return fail(B200MOE_ERR_SHAPE, "%s: block_m must be %d (the gathering kernel is one-CTA)", name, kBlockM);
+  if (hidden % kBlockK != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld must be a multiple of %d", name, (long long)hidden, kBlockK);
+  if (inter % (kBlockN / 2) != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: intermediate size %lld must be a multiple of %d", name,
+                (long long)inter, kBlockN / 2);
+  if (top_k < 1 || num_tokens < 0 || num_tokens > 0x7fffffffLL)
+    return fail(B200MOE_ERR_SHAPE, "%s: top_k=%d num_tokens=%lld", name, top_k, (long long)num_tokens);
+  if (sorted_capacity < block_m || num_tokens == 0) return B200MOE_OK;
+  if (!tokens || !sorted_token_ids || !w13 || !act || !expert_ids || !num_tokens_post_pad)
+    return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
+  if (!aligned_to(tokens, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16) ||
+      !aligned_to(sorted_token_ids, 16))
+    return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap(&ta, tokens, num_tokens, hidden, 1, name)) return rc;  // one row per box
+  if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden,
+                         kBlockN / 2, name))
+    return rc;
+  GemmParams p{};
+  p.expert_ids = expert_ids;
+  p.npp = num_tokens_post_pad;
+  p.sorted = sorted_token_ids;
+  p.out = static_cast<__nv_bfloat16*>(act);
+  p.capacity = sorted_capacity;
+  p.num_experts = num_experts;
+  p.k_blocks = static_cast<int>(hidden / kBlockK);
+  p.n_tiles = static_cast<int>(inter / (kBlockN / 2));
+  p.b_rows_per_expert = static_cast<int>(2 * inter);
+  p.inter = static_cast<int>(inter);
+  p.out_ld = inter;
+  p.top_k = top_k;
+  p.num_src_rows = static_cast<int>(num_tokens);
+  return launch<kW13Gather>(ta, tb, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, void* out,

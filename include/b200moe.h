@@ -209,6 +209,23 @@ int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void* w13, void*
                                     b200moe_stream_t stream);
 
 /*
+ * The same GEMM with the row gather folded in: the A rows are fetched straight from the token
+ * tensor by TMA row gathers (cp.async.bulk.tensor tile::gather4, four rows per instruction,
+ * a_row(s) = sorted_token_ids[s] / top_k), which is the reference kernel's A addressing
+ * (layers/moe/fused_moe.py:88-91) without a separate gather pass or an expert-sorted copy.
+ * Padding slots read row 0; their results are never consumed.  block_m must be 128.
+ *
+ *   tokens  bf16 [num_tokens, hidden];  sorted_token_ids i32 [sorted_capacity], 16-byte aligned
+ */
+int b200moe_grouped_gemm_w13_swiglu_gather(const void* tokens, int64_t num_tokens, int top_k,
+                                           const int32_t* sorted_token_ids, const void* w13,
+                                           void* act, const int32_t* expert_ids,
+                                           const int32_t* num_tokens_post_pad,
+                                           int64_t sorted_capacity, int num_experts,
+                                           int64_t hidden, int64_t inter, int block_m,
+                                           b200moe_stream_t stream);
+
+/*
  * Grouped expert GEMM 2 with the routing-weight epilogue:
  *   out[p, n] = bf16( topk_weights[p] * sum_k act[s, k] * w2[e, n, k] ),  p = sorted_token_ids[s]
  * for every slot s holding a pair; rows of out are indexed by the flat pair index p, i.e. out is

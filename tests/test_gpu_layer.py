@@ -97,6 +97,37 @@ def test_grouped_gemm_w2_scale(T, H, I, E, block_m):
     assert st["rel_fro"] < 4e-3 and st["max_abs"] < 2e-2 * max(st["ref_max_abs"], 1.0), st
 
 
+@pytest.mark.parametrize("T,H,I,E,k", [(100, 256, 128, 8, 2), (1000, 1024, 512, 8, 2), (37, 64, 256, 3, 2),
+                                       (513, 512, 256, 8, 1)])
+def test_grouped_gemm_w13_gather_matches_pregathered_rows(T, H, I, E, k):
+    """TMA row gathers inside the GEMM must give bit for bit what a separate gather pass gives."""
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(T * 7 + H)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).to(torch.bfloat16).to(DEV)
+    ids = torch.randint(0, E, (T * k,), generator=g, dtype=torch.int32)
+    s, e, n = aligned(ids.numpy(), E)
+    cap, used = s.size, int(n[0])
+    d_s, d_e, d_n = torch.from_numpy(s).to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    a_sorted = torch.empty(cap, H, dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.b200moe_gather_rows(x.data_ptr(), a_sorted.data_ptr(), d_s.data_ptr(),
+                                       d_n.data_ptr(), cap, T, H, k, stream), "gather_rows")
+    act0 = torch.full((cap, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    act1 = torch.full((cap, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(a_sorted.data_ptr(), w13.data_ptr(), act0.data_ptr(),
+                                                   d_e.data_ptr(), d_n.data_ptr(), cap, E, H, I, 128,
+                                                   stream), "w13")
+    _lib.check(lib.b200moe_grouped_gemm_w13_swiglu_gather(
+        x.data_ptr(), T, k, d_s.data_ptr(), w13.data_ptr(), act1.data_ptr(), d_e.data_ptr(),
+        d_n.data_ptr(), cap, E, H, I, 128, stream), "w13 gather")
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    live = torch.from_numpy(s[:used] >= 0).to(DEV)
+    assert torch.equal(act0[:used][live], act1[:used][live])   # padding rows may differ: unused
+    assert (act1[used:] == 9.0).all()
+
+
 # --------------------------------------------------------------------------------- whole layer
 def run_layer(inp, wl, inplace=True):
     x = inp["x"].to(torch.bfloat16).to(DEV).clone()
