@@ -4,12 +4,11 @@
 Function names, arguments and results follow the reference's layers/moe/fused_moe.py
 (``fused_topk`` :130-164, ``fused_experts`` :170-293).  The reference runs about five torch
 kernels for routing, four launches for alignment, two Triton GEMMs, ``silu_and_mul`` and
-``moe_sum``; here one call is five C-ABI calls (alignment is one launch for decode-sized batches
+``moe_sum``; here one call is six C-ABI calls (alignment is one launch for decode-sized batches
 and three for long ones):
 
-    topk_softmax (renormalising) -> align_block_size (writes its own padding)
-    -> grouped_gemm_w13_swiglu_gather (TMA row gathers feed the A operand)
-    -> grouped_gemm_w2_scale -> moe_sum
+    topk_softmax (renormalising) -> align_block_size (writes its own padding) -> gather_rows
+    -> grouped_gemm_w13_swiglu -> grouped_gemm_w2_scale -> moe_sum
 """
 from __future__ import annotations
 
@@ -52,21 +51,6 @@ def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: i
     return topk_weights, topk_ids
 
 
-class _Buffers(dict):
-    """The scratch tensors of one shape; the expert-sorted copy of the tokens is only needed by
-    the two-CTA tiling and is allocated on first use."""
-
-    def __init__(self, tensors: dict, hidden: int):
-        super().__init__(tensors)
-        self._hidden = hidden
-
-    def a_sorted(self) -> torch.Tensor:
-        if "a_sorted" not in self:
-            self["a_sorted"] = torch.empty(self["capacity"], self._hidden, dtype=torch.bfloat16,
-                                           device=self["act"].device)
-        return self["a_sorted"]
-
-
 class _Workspace:
     """Scratch tensors of one ``fused_experts`` call, kept per (device, shape) so that steady-state
     calls allocate nothing.  The reference allocates its three caches on every call
@@ -87,7 +71,7 @@ class _Workspace:
             blocks = (capacity + block_m - 1) // block_m
             i32 = dict(dtype=torch.int32, device=device)
             bf16 = dict(dtype=torch.bfloat16, device=device)
-            ws = _Buffers({
+            ws = {
                 "capacity": capacity,
                 "topk_weights": torch.empty(num_tokens, topk, dtype=torch.float32, device=device),
                 "topk_ids": torch.empty(num_tokens, topk, **i32),
@@ -95,9 +79,10 @@ class _Workspace:
                 "expert_ids": torch.zeros(blocks, **i32),
                 "num_post_pad": torch.zeros(1, **i32),
                 "align_ws": torch.empty(max(_C.align_workspace_numel(pairs, num_experts), 1), **i32),
+                "a_sorted": torch.empty(capacity, hidden, **bf16),
                 "act": torch.empty(capacity, inter, **bf16),
                 "cache3": torch.empty(num_tokens, topk, hidden, **bf16),
-            }, hidden)
+            }
             self._cache[key] = ws
         return ws
 
@@ -192,25 +177,20 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
             _C.moe_align_block_size(ws["topk_ids"], num_experts, block_m, ws["sorted_ids"],
                                     ws["expert_ids"], ws["num_post_pad"], fill_pads=True,
                                     workspace=ws["align_ws"])
-        if block_m == BLOCK_SIZE_M:
-            # One-CTA tiles: the first GEMM gathers its A rows itself (TMA row gathers).
-            with _timed("grouped_gemm_w13_swiglu"):
-                _lib.check(lib.b200moe_grouped_gemm_w13_swiglu_gather(
-                    hidden_states.data_ptr(), num_tokens, topk, ws["sorted_ids"].data_ptr(),
-                    w1.data_ptr(), ws["act"].data_ptr(), ws["expert_ids"].data_ptr(),
-                    ws["num_post_pad"].data_ptr(), capacity, num_experts, hidden, inter, block_m,
-                    stream), "grouped_gemm_w13_swiglu_gather")
-        else:
-            with _timed("gather_rows"):
-                _lib.check(lib.b200moe_gather_rows(
-                    hidden_states.data_ptr(), ws.a_sorted().data_ptr(), ws["sorted_ids"].data_ptr(),
-                    ws["num_post_pad"].data_ptr(), capacity, num_tokens, hidden, topk, stream),
-                    "gather_rows")
-            with _timed("grouped_gemm_w13_swiglu"):
-                _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
-                    ws.a_sorted().data_ptr(), w1.data_ptr(), ws["act"].data_ptr(),
-                    ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
-                    num_experts, hidden, inter, block_m, stream), "grouped_gemm_w13_swiglu")
+        # The A rows are gathered into expert-sorted order once, then read as dense TMA tiles.
+        # (b200moe_grouped_gemm_w13_swiglu_gather folds the gather into the GEMM with TMA
+        # tile::gather4, but 32 four-row gathers per K step run the kernel 2.6x slower than one
+        # tiled box on B200, so the layer does not use it.)
+        with _timed("gather_rows"):
+            _lib.check(lib.b200moe_gather_rows(
+                hidden_states.data_ptr(), ws["a_sorted"].data_ptr(), ws["sorted_ids"].data_ptr(),
+                ws["num_post_pad"].data_ptr(), capacity, num_tokens, hidden, topk, stream),
+                "gather_rows")
+        with _timed("grouped_gemm_w13_swiglu"):
+            _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
+                ws["a_sorted"].data_ptr(), w1.data_ptr(), ws["act"].data_ptr(),
+                ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity, num_experts,
+                hidden, inter, block_m, stream), "grouped_gemm_w13_swiglu")
         with _timed("grouped_gemm_w2_scale"):
             _lib.check(lib.b200moe_grouped_gemm_w2_scale(
                 ws["act"].data_ptr(), w2.data_ptr(), ws["cache3"].data_ptr(),
@@ -218,7 +198,7 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
                 ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
                 num_tokens * topk, num_experts, hidden, inter, block_m, stream),
                 "grouped_gemm_w2_scale")
-        _lib.count_launches(2 if block_m == BLOCK_SIZE_M else 3)
+        _lib.count_launches(3)
         with _timed("moe_sum"):
             _C.moe_sum(ws["cache3"], output)
     return output
