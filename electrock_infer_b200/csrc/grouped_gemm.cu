@@ -182,6 +182,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
+// 32 lanes x 16 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -195,9 +206,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 // Instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) |
-                                (static_cast<uint32_t>(kBlockN >> 3) << 17) |
-                                (static_cast<uint32_t>(kBlockM >> 4) << 24);
+constexpr uint32_t make_instr_desc(int n, int m) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+constexpr uint32_t kInstrDesc = make_instr_desc(kBlockN, kBlockM);
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -238,6 +251,9 @@ struct GemmParams {
   int b_rows_per_expert;         // kW13: 2 * inter; kW2: hidden
   int inter;                     // kW13: offset of the up rows inside an expert's w13
   long long out_ld;              // leading dimension of out in elements
+  int half_n;                    // kW13 (one-CTA kernel): gate columns per tile; the MMA is 2*half_n wide
+  uint32_t idesc;                // one-CTA kernel: instruction descriptor for that width
+  int stage_tx_bytes;            // one-CTA kernel: bytes the TMA loads of one stage deliver
   int top_k;                     // kW13Gather: A row of slot s is sorted[s] / top_k
   int num_src_rows;              // kW13Gather: rows of the token tensor
 };
@@ -312,7 +328,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool ok = true;
     for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
-      const int b_row0 = c.expert * p.b_rows_per_expert + c.n_tile * (kBlockN / 2);
+      const int b_row0 = c.expert * p.b_rows_per_expert + c.n_tile * p.half_n;
       int rows[4];
       {
         const int4 ids = *reinterpret_cast<const int4*>(
@@ -328,7 +344,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int good = 1;
         if (lane == 0) {
           good = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x101) ? 1 : 0;
-          if (good) mbar_expect_tx(&full_bar[stage], kStageBytes);
+          if (good) mbar_expect_tx(&full_bar[stage], p.stage_tx_bytes);
         }
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) { ok = false; break; }
@@ -338,7 +354,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (lane == 0) {
           uint8_t* sb = sa + kABytes;
           tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
-          tma_load_2d(sb + kBBytes / 2, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0 + p.inter);
+          tma_load_2d(sb + p.half_n * (kBlockK * 2), &tmap_b, &full_bar[stage], kb * kBlockK,
+                      b_row0 + p.inter);
         }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
@@ -354,16 +371,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off);
         const int a_row = c.m_block * kBlockM;
         const int b_row0 = c.expert * p.b_rows_per_expert +
-                           c.n_tile * (kIsW13 ? kBlockN / 2 : kBlockN);
+                           c.n_tile * (kIsW13 ? p.half_n : kBlockN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x101)) { ok = false; break; }
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
-          mbar_expect_tx(&full_bar[stage], kStageBytes);
+          mbar_expect_tx(&full_bar[stage], p.stage_tx_bytes);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBlockK, a_row);
           if (kIsW13) {
+            // Gate rows, then the matching up rows directly behind them: one B operand of
+            // 2 * half_n rows.
             tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
-            tma_load_2d(sb + kBBytes / 2, &tmap_b, &full_bar[stage], kb * kBlockK,
+            tma_load_2d(sb + p.half_n * (kBlockK * 2), &tmap_b, &full_bar[stage], kb * kBlockK,
                         b_row0 + p.inter);
           } else {
             tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
@@ -394,7 +413,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             const uint64_t adesc = make_smem_desc(sa + k * kUmmaK * 2);
             const uint64_t bdesc = make_smem_desc(sb + k * kUmmaK * 2);
-            umma_bf16(tmem_d, adesc, bdesc, kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16(tmem_d, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage when these MMAs are done
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -422,26 +441,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * kBlockN);
       if (kIsW13) {
-        __nv_bfloat16* dst = p.out + slot * p.out_ld + static_cast<long long>(c.n_tile) * (kBlockN / 2);
+        __nv_bfloat16* dst = p.out + slot * p.out_ld + static_cast<long long>(c.n_tile) * p.half_n;
+        const int chunks = p.half_n / 16;
 #pragma unroll 1
-        for (int ch = 0; ch < (kBlockN / 2) / 32; ++ch) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + ch * 32, g);
-          tmem_ld_32x32(taddr + kBlockN / 2 + ch * 32, u);
+        for (int ch = 0; ch < chunks; ++ch) {
+          uint32_t g[16], u[16];
+          tmem_ld_32x16(taddr + ch * 16, g);
+          tmem_ld_32x16(taddr + p.half_n + ch * 16, u);
           tmem_ld_wait();
-          uint32_t o[16];
+          uint32_t o[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < 8; ++j) {
             const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
             const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
             const float a0 = g0 / (1.0f + __expf(-g0)) * u0;
             const float a1 = g1 / (1.0f + __expf(-g1)) * u1;
             o[j] = pack_bf16(a0, a1);
           }
-          uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            d4[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+          uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 16);
+          d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       } else {
         const int pair = p.sorted[slot];
@@ -848,6 +867,36 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   return check_launch("grouped_gemm (2-CTA)");
 }
 
+// Gate columns per tile for the one-CTA w13 kernel.  With many tiles per SM the full 128 is best
+// (the MMA is most efficient at N = 256).  With few M blocks (decode-sized batches, where the
+// kernel streams weights and is HBM-bound) the tile count rarely divides by the SM count, so a
+// narrower tile that fills the last wave better wins: e.g. 8 M blocks x 14336 / 128 = 896 tiles is
+// 6.05 waves of 148 SMs, while 14336 / 112 gives 1024 tiles = 6.92 waves of smaller tiles.
+int choose_half_n(int64_t capacity, int num_experts, int64_t inter) {
+  const int64_t pairs = capacity - static_cast<int64_t>(num_experts) * (kBlockM - 1);
+  const int64_t per_expert = pairs > 0 ? ceil_div64(pairs, num_experts) : 1;
+  const int64_t blocks = per_expert <= 2 * kBlockM
+                             ? num_experts * ceil_div64(per_expert, kBlockM)
+                             : ceil_div64(pairs, kBlockM) + num_experts / 2;
+  const int sms = sm_count();
+  if (blocks * (inter / (kBlockN / 2)) >= 16ll * sms) return kBlockN / 2;
+  int best = kBlockN / 2;
+  int64_t best_cost = -1;
+  for (int h = kBlockN / 2; h >= 64; h -= 16) {
+    if (inter % h != 0) continue;
+    const int64_t waves = ceil_div64(blocks * (inter / h), sms);
+    const int64_t cost = waves * (2 * h + 16);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = h; }
+  }
+  return best;
+}
+
+// Fills the fields of the one-CTA kernel that depend on the accumulator width.
+void set_width(GemmParams* p, int mma_n) {
+  p->idesc = make_instr_desc(mma_n, kBlockM);
+  p->stage_tx_bytes = kABytes + mma_n * kBlockK * 2;
+}
+
 int check_common(const char* name, int num_experts, int64_t hidden, int64_t inter, int block_m,
                  int64_t capacity) {
   if (block_m != kBlockM && block_m != kPairBlockM)
@@ -884,10 +933,13 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(a_sorted, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
+  // The two-CTA kernel has a fixed 128 + 128 column tile; the one-CTA kernel picks its width.
+  const int half_n = block_m == kPairBlockM ? kBlockN / 2
+                                            : choose_half_n(sorted_capacity, num_experts, inter);
   CUtensorMap ta, tb;
   if (int rc = make_tmap(&ta, a_sorted, sorted_capacity, hidden, kBlockM, name)) return rc;
-  if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden,
-                         kBlockN / 2, name))
+  if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden, half_n,
+                         name))
     return rc;
   GemmParams p{};
   p.expert_ids = expert_ids;
@@ -896,10 +948,12 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   p.capacity = sorted_capacity;
   p.num_experts = num_experts;
   p.k_blocks = static_cast<int>(hidden / kBlockK);
-  p.n_tiles = static_cast<int>(inter / (kBlockN / 2));
+  p.n_tiles = static_cast<int>(inter / half_n);
   p.b_rows_per_expert = static_cast<int>(2 * inter);
   p.inter = static_cast<int>(inter);
   p.out_ld = inter;
+  p.half_n = half_n;
+  set_width(&p, 2 * half_n);
   if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
 }
@@ -928,9 +982,10 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu_gather(
       !aligned_to(sorted_token_ids, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
   CUtensorMap ta, tb;
+  const int half_n = choose_half_n(sorted_capacity, num_experts, inter);
   if (int rc = make_tmap(&ta, tokens, num_tokens, hidden, 1, name)) return rc;  // one row per box
-  if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden,
-                         kBlockN / 2, name))
+  if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden, half_n,
+                         name))
     return rc;
   GemmParams p{};
   p.expert_ids = expert_ids;
@@ -940,10 +995,12 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu_gather(
   p.capacity = sorted_capacity;
   p.num_experts = num_experts;
   p.k_blocks = static_cast<int>(hidden / kBlockK);
-  p.n_tiles = static_cast<int>(inter / (kBlockN / 2));
+  p.n_tiles = static_cast<int>(inter / half_n);
   p.b_rows_per_expert = static_cast<int>(2 * inter);
   p.inter = static_cast<int>(inter);
   p.out_ld = inter;
+  p.half_n = half_n;
+  set_width(&p, 2 * half_n);
   p.top_k = top_k;
   p.num_src_rows = static_cast<int>(num_tokens);
   return launch<kW13Gather>(ta, tb, p, static_cast<cudaStream_t>(stream));
@@ -991,6 +1048,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   p.b_rows_per_expert = static_cast<int>(hidden);
   p.inter = 0;
   p.out_ld = hidden;
+  set_width(&p, kBlockN);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
 }
