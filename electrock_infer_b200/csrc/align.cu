@@ -185,6 +185,8 @@ align_single_cta_kernel(const T* __restrict__ ids, int64_t numel, int num_expert
   __shared__ int s_total[kMaxExperts];
   __shared__ int s_cumsum[kMaxExperts + 1];
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // Contiguous range per warp, a multiple of the 128-id warp step.
   const int64_t steps = ceil_div64(numel, kIdsPerWarpStep);
@@ -254,6 +256,8 @@ __global__ void __launch_bounds__(kSegThreads)
 align_count_kernel(const T* __restrict__ ids, int64_t numel, int num_experts,
                    int32_t* __restrict__ seg_counts) {
   __shared__ int s_cnt[kSegWarps][kMaxExperts];
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t seg_begin = static_cast<int64_t>(blockIdx.x) * kSegment;
   const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * kIdsPerSegWarp, numel);
@@ -299,6 +303,8 @@ align_scan_kernel(int32_t* __restrict__ seg_counts, int64_t num_segments, int nu
   __shared__ int s_cumsum[kMaxExperts + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x < kMaxExperts) s_carry[threadIdx.x] = 0;
+  pdl_wait();
+  pdl_launch_dependents();
   __syncthreads();
   for (int64_t base = 0; base < num_segments; base += kThreads) {
     const int64_t seg = base + threadIdx.x;
@@ -372,6 +378,8 @@ align_scatter_kernel(const T* __restrict__ ids, int64_t numel, int num_experts, 
   __shared__ int s_off[kMaxExperts + 1];         // padded offsets of the whole input
   __shared__ int32_t s_sorted[kSegment];
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t seg_begin = static_cast<int64_t>(blockIdx.x) * kSegment;
   const int64_t begin = min(seg_begin + static_cast<int64_t>(warp) * kIdsPerSegWarp, numel);
@@ -490,8 +498,8 @@ int run(const void* ids_v, int64_t numel, int E, int bs, int32_t* sorted, int64_
         cudaStream_t st) {
   const T* ids = static_cast<const T*>(ids_v);
   if (numel <= kSinglePassMax) {
-    align_single_cta_kernel<T><<<1, kThreads, 0, st>>>(ids, numel, E, bs, sorted, cap, expert_ids,
-                                                       npp, offsets, fill);
+    launch_pdl(align_single_cta_kernel<T>, dim3(1), dim3(kThreads), 0, st, ids, numel, E, bs,
+               sorted, cap, expert_ids, npp, offsets, fill);
     return check_launch("moe_align_block_size");
   }
   const size_t need = b200moe_align_workspace_bytes(numel, E);
@@ -504,10 +512,13 @@ int run(const void* ids_v, int64_t numel, int E, int bs, int32_t* sorted, int64_
   const int64_t nseg = ceil_div64(numel, kSegment);
   int32_t* seg = static_cast<int32_t*>(ws);
   int32_t* meta = seg + nseg * kMaxExperts;
-  align_count_kernel<T><<<static_cast<unsigned>(nseg), kSegThreads, 0, st>>>(ids, numel, E, seg);
-  align_scan_kernel<<<1, kThreads, 0, st>>>(seg, nseg, E, bs, meta, npp, offsets);
-  align_scatter_kernel<T><<<static_cast<unsigned>(nseg), kSegThreads, 0, st>>>(
-      ids, numel, E, bs, seg, meta, sorted, cap, expert_ids, fill);
+  const dim3 segs(static_cast<unsigned>(nseg));
+  launch_pdl(align_count_kernel<T>, segs, dim3(kSegThreads), 0, st, ids, numel, E, seg);
+  launch_pdl(align_scan_kernel, dim3(1), dim3(kThreads), 0, st, seg, nseg, E, bs, meta, npp,
+             offsets);
+  launch_pdl(align_scatter_kernel<T>, segs, dim3(kSegThreads), 0, st, ids, numel, E, bs,
+             static_cast<const int32_t*>(seg), static_cast<const int32_t*>(meta), sorted, cap,
+             expert_ids, fill);
   return check_launch("moe_align_block_size");
 }
 

@@ -30,6 +30,31 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 
 __host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch.  Every kernel of the layer is launched with the
+// programmatic-stream-serialization attribute: it may begin (block scheduling, prologue) while
+// its predecessor in the stream is still draining, and must call pdl_wait() before it touches
+// global memory the predecessor wrote.  pdl_launch_dependents() lets the successor do the same.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // 16-byte global load that bypasses L1 allocation: for data that is read exactly once.
 __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
   uint4 v;

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(kThreads)
 gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                    const int32_t* __restrict__ sorted, const int32_t* __restrict__ npp_ptr,
                    int64_t capacity, int64_t num_src_rows, int row_vecs, int top_k) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t npp = min(static_cast<int64_t>(*npp_ptr), capacity);
   const int group = threadIdx.x / (kThreads / kRowsPerCta);
   const int t = threadIdx.x % (kThreads / kRowsPerCta);
@@ -93,8 +95,9 @@ extern "C" int b200moe_gather_rows(const void* src, void* dst, const int32_t* so
   int64_t grid = ceil_div64(sorted_capacity, kRowsPerCta);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   if (grid > cap) grid = cap;
-  gather_rows_kernel<<<static_cast<unsigned>(grid), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(src), static_cast<uint4*>(dst), sorted_token_ids,
-      num_tokens_post_pad, sorted_capacity, num_src_rows, static_cast<int>(row_elems / 8), top_k);
+  launch_pdl(gather_rows_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0,
+             static_cast<cudaStream_t>(stream), static_cast<const uint4*>(src),
+             static_cast<uint4*>(dst), sorted_token_ids, num_tokens_post_pad, sorted_capacity,
+             num_src_rows, static_cast<int>(row_elems / 8), top_k);
   return check_launch("gather_rows");
 }

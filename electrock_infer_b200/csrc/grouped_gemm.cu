@@ -295,6 +295,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tmem_relinquish();
   }
   __syncthreads();
+  pdl_wait();  // everything above touched only this CTA's shared and tensor memory
+  pdl_launch_dependents();
   long long npp = *p.npp;
   if (npp > p.capacity) npp = p.capacity;
   const int num_blocks = static_cast<int>(npp / kBlockM);
@@ -634,6 +636,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tmem_alloc_pair(&tmem_slot, kTmemCols);
     tmem_relinquish_pair();
   }
+  pdl_wait();  // everything above touched only this CTA's shared and tensor memory
+  pdl_launch_dependents();
   long long npp = *p.npp;
   if (npp > p.capacity) npp = p.capacity;
   const int num_blocks = static_cast<int>(npp / kPairBlockM);
@@ -851,7 +855,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cu
   if (attr_err != cudaSuccess)
     return fail(B200MOE_ERR_CUDA, "grouped_gemm: cannot reserve %d bytes of shared memory: %s",
                 kSmemBytes, cudaGetErrorString(attr_err));
-  grouped_gemm_kernel<kMode><<<sm_count(), kThreads, kSmemBytes, st>>>(ta, tb, p);
+  launch_pdl(grouped_gemm_kernel<kMode>, dim3(sm_count()), dim3(kThreads), kSmemBytes, st, ta, tb, p);
   return check_launch("grouped_gemm");
 }
 
@@ -863,7 +867,8 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
     return fail(B200MOE_ERR_CUDA, "grouped_gemm: cannot reserve %d bytes of shared memory: %s",
                 kPairSmemBytes, cudaGetErrorString(attr_err));
   const int grid = sm_count() & ~1;  // whole clusters of two CTAs
-  grouped_gemm_pair_kernel<kMode><<<grid, kThreads, kPairSmemBytes, st>>>(ta, tb, p);
+  launch_pdl(grouped_gemm_pair_kernel<kMode>, dim3(grid), dim3(kThreads), kPairSmemBytes, st, ta,
+             tb, p);
   return check_launch("grouped_gemm (2-CTA)");
 }
 

@@ -62,6 +62,8 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 topk_softmax_kernel(const T* __restrict__ logits, float* __restrict__ weights,
                     int32_t* __restrict__ indices, int64_t num_tokens, int renormalize) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int half = threadIdx.x & 1;
   const int pair = threadIdx.x >> 1;
   const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + pair;
@@ -136,8 +138,8 @@ topk_softmax_kernel(const T* __restrict__ logits, float* __restrict__ weights,
 template <typename T>
 int launch(const void* logits, float* w, int32_t* ids, int64_t T_, int renorm, cudaStream_t st) {
   const int64_t grid = ceil_div64(T_, kRowsPerCta);
-  topk_softmax_kernel<T><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(
-      static_cast<const T*>(logits), w, ids, T_, renorm);
+  launch_pdl(topk_softmax_kernel<T>, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, st,
+             static_cast<const T*>(logits), w, ids, T_, renorm);
   return check_launch("topk_softmax");
 }
 
