@@ -6,7 +6,7 @@
 
 One step is one pass of the layer over one batch of seeded synthetic tokens.  At one GPU the
 workload is the prefill-sized, skew-routed Mixtral layer (T=8192); at N > 1 it is the T=16384 step
-sharded tensor-parallel (as the reference does) or expert-parallel.  Rank 0 prints ONE JSON line:
+sharded expert-parallel (default) or tensor-parallel as the reference does (--parallel tp).  Rank 0 prints ONE JSON line:
 
   value         tokens/s with inputs resident in HBM (CUDA events around K steps, max over ranks)
   e2e           the same through host buffers: pinned H2D of activations and logits and D2H of the
@@ -174,7 +174,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--parallel", choices=["tp", "ep"], default="tp")
+    ap.add_argument("--parallel", choices=["tp", "ep"], default="ep")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--block-m", type=int, default=None, choices=[128, 256],
@@ -304,11 +304,19 @@ def main():
         # ---- end to end through host buffers: every step copies its inputs from pinned host
         # memory and copies its result back; copies and compute run on three streams with two
         # device buffers, so step i+1's upload and step i-1's download overlap step i's kernels.
-        xh = x0.cpu().pin_memory()
-        lh = logits.cpu().pin_memory()
+        # Tensor parallel needs the same activations on every rank: each rank uploads 1/N of the
+        # batch and the ranks all-gather over NVLink, and each rank downloads 1/N of the (replicated)
+        # result.  Expert parallel is token-sharded to begin with.
+        tp_split = layer_cls is None and world > 1
+        t_loc = x0.shape[0] // world if tp_split else x0.shape[0]
+        lo = rank * t_loc if tp_split else 0
+        xh = x0[lo:lo + t_loc].cpu().pin_memory()
+        lh = logits[lo:lo + t_loc].cpu().pin_memory()
         oh = [torch.empty_like(xh).pin_memory() for _ in range(2)]
         xd = [torch.empty_like(x0) for _ in range(2)]
         ld = [torch.empty_like(logits) for _ in range(2)]
+        xs = [torch.empty_like(x0[:t_loc]) for _ in range(2)] if tp_split else xd
+        ls = [torch.empty_like(logits[:t_loc]) for _ in range(2)] if tp_split else ld
         s_in, s_c, s_out = (torch.cuda.Stream(dev) for _ in range(3))
         ev_in = [torch.cuda.Event() for _ in range(2)]
         ev_done = [torch.cuda.Event() for _ in range(2)]
@@ -322,8 +330,11 @@ def main():
                 b = i & 1
                 with torch.cuda.stream(s_in):
                     s_in.wait_event(ev_out[b])   # the result that aliases xd[b] has been downloaded
-                    xd[b].copy_(xh, non_blocking=True)
-                    ld[b].copy_(lh, non_blocking=True)
+                    xs[b].copy_(xh, non_blocking=True)
+                    ls[b].copy_(lh, non_blocking=True)
+                    if tp_split:
+                        dist.all_gather_into_tensor(xd[b], xs[b])
+                        dist.all_gather_into_tensor(ld[b], ls[b])
                     ev_in[b].record(s_in)
                 with torch.cuda.stream(s_c):
                     s_c.wait_event(ev_in[b])
@@ -331,7 +342,7 @@ def main():
                     ev_done[b].record(s_c)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_done[b])
-                    oh[b].copy_(out, non_blocking=True)
+                    oh[b].copy_(out[lo:lo + t_loc], non_blocking=True)
                     ev_out[b].record(s_out)
             for st in (s_in, s_c, s_out):
                 main.wait_stream(st)
@@ -415,8 +426,8 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(wl, args, world),
         "e2e": {"value": e2e_value, "unit": UNIT,
-                "h2d_bytes_per_step": xh.numel() * 2 + lh.numel() * 4,
-                "d2h_bytes_per_step": oh[0].numel() * 2,
+                "h2d_bytes_per_step": (xh.numel() * 2 + lh.numel() * 4) * world,
+                "d2h_bytes_per_step": oh[0].numel() * 2 * world,
                 "overlap": "3 streams, 2 device buffers: uploads/downloads overlap the kernels"},
         "gpu_launches": launches,
         "roofline": roofline,
