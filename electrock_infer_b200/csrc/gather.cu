@@ -35,6 +35,47 @@ gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
   }
 }
 
+// Row gather whose source rows live on several GPUs: token row r is row r % rows_per_rank of the
+// tensor at srcs[r / rows_per_rank] (plain loads through peer mappings).  This is the dispatch
+// step of the expert-parallel layer done as a pull by the GPU that owns the expert.
+__global__ void __launch_bounds__(kThreads)
+gather_rows_peer_kernel(const uint4* const* __restrict__ srcs, uint4* __restrict__ dst,
+                        const int32_t* __restrict__ sorted, const int32_t* __restrict__ npp_ptr,
+                        int64_t capacity, int num_ranks, int64_t rows_per_rank, int row_vecs,
+                        int top_k) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t npp = min(static_cast<int64_t>(*npp_ptr), capacity);
+  const int group = threadIdx.x / (kThreads / kRowsPerCta);
+  const int t = threadIdx.x % (kThreads / kRowsPerCta);
+  for (int64_t s = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + group; s < npp;
+       s += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
+    const int id = sorted[s];
+    const int64_t row = id >= 0 ? id / top_k : -1;
+    const int64_t rank = row >= 0 ? row / rows_per_rank : num_ranks;
+    uint4* d = dst + s * row_vecs;
+    if (rank < num_ranks) {
+      const uint4* p = srcs[rank] + (row - rank * rows_per_rank) * row_vecs;
+      // Several loads in flight per thread: a peer load costs a few microseconds.
+      for (int c = t; c < row_vecs; c += 4 * (kThreads / kRowsPerCta)) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int cc = c + u * (kThreads / kRowsPerCta);
+          if (cc < row_vecs) v[u] = p[cc];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int cc = c + u * (kThreads / kRowsPerCta);
+          if (cc < row_vecs) d[cc] = v[u];
+        }
+      }
+    } else {
+      for (int c = t; c < row_vecs; c += kThreads / kRowsPerCta) d[c] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
 // dst[index[i], :] = src[i, :] for i < num_rows; entries with an index outside [0, num_dst_rows)
 // are skipped.
 __global__ void __launch_bounds__(kThreads)
@@ -75,6 +116,33 @@ extern "C" int b200moe_scatter_rows(const void* src, void* dst, const int32_t* i
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, num_rows, num_dst_rows,
       static_cast<int>(row_elems / 8));
   return check_launch("scatter_rows");
+}
+
+extern "C" int b200moe_gather_rows_peer(const void* const* src_table, int num_ranks,
+                                        int64_t rows_per_rank, void* dst,
+                                        const int32_t* sorted_token_ids,
+                                        const int32_t* num_tokens_post_pad, int64_t sorted_capacity,
+                                        int64_t row_elems, int top_k, b200moe_stream_t stream) {
+  using namespace b200moe;
+  if (row_elems <= 0 || row_elems % 8 != 0)
+    return fail(B200MOE_ERR_SHAPE, "gather_rows_peer: row_elems=%lld must be a positive multiple of 8",
+                (long long)row_elems);
+  if (top_k < 1 || num_ranks < 1 || rows_per_rank < 1)
+    return fail(B200MOE_ERR_SHAPE, "gather_rows_peer: top_k=%d num_ranks=%d rows_per_rank=%lld", top_k,
+                num_ranks, (long long)rows_per_rank);
+  if (sorted_capacity < 0) return fail(B200MOE_ERR_SHAPE, "gather_rows_peer: negative size");
+  if (sorted_capacity == 0) return B200MOE_OK;
+  if (!src_table || !dst || !sorted_token_ids || !num_tokens_post_pad)
+    return fail(B200MOE_ERR_NULL, "gather_rows_peer: null pointer");
+  if (!aligned_to(dst, 16)) return fail(B200MOE_ERR_ALIGN, "gather_rows_peer: dst must be 16-byte aligned");
+  int64_t grid = ceil_div64(sorted_capacity, kRowsPerCta);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (grid > cap) grid = cap;
+  launch_pdl(gather_rows_peer_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0,
+             static_cast<cudaStream_t>(stream), reinterpret_cast<const uint4* const*>(src_table),
+             static_cast<uint4*>(dst), sorted_token_ids, num_tokens_post_pad, sorted_capacity,
+             num_ranks, rows_per_rank, static_cast<int>(row_elems / 8), top_k);
+  return check_launch("gather_rows_peer");
 }
 
 extern "C" int b200moe_gather_rows(const void* src, void* dst, const int32_t* sorted_token_ids,

@@ -254,6 +254,8 @@ struct GemmParams {
   int half_n;                    // kW13 (one-CTA kernel): gate columns per tile; the MMA is 2*half_n wide
   uint32_t idesc;                // one-CTA kernel: instruction descriptor for that width
   int stage_tx_bytes;            // one-CTA kernel: bytes the TMA loads of one stage deliver
+  __nv_bfloat16* const* out_table;  // kW2, optional: per-rank output bases (peer mappings)
+  long long pairs_per_rank;      // kW2 with out_table: pair p is row p % pairs_per_rank of rank p / ...
   int top_k;                     // kW13Gather: A row of slot s is sorted[s] / top_k
   int num_src_rows;              // kW13Gather: rows of the token tensor
 };
@@ -468,8 +470,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int pair = p.sorted[slot];
         const bool live = pair >= 0 && pair < p.num_pairs;
         const float w = live ? p.topk_weights[pair] : 0.f;
-        __nv_bfloat16* dst = p.out + static_cast<long long>(live ? pair : 0) * p.out_ld +
-                             static_cast<long long>(c.n_tile) * kBlockN;
+        // With an output table the row goes straight to the GPU that owns the token (a plain
+        // store through a peer mapping): the return all-to-all is this epilogue.
+        __nv_bfloat16* base = p.out;
+        long long out_row = live ? pair : 0;
+        if (p.out_table != nullptr && live) {
+          const long long owner = out_row / p.pairs_per_rank;
+          base = p.out_table[owner];
+          out_row -= owner * p.pairs_per_rank;
+        }
+        __nv_bfloat16* dst = base + out_row * p.out_ld + static_cast<long long>(c.n_tile) * kBlockN;
 #pragma unroll 1
         for (int ch = 0; ch < kBlockN / 32; ++ch) {
           uint32_t v[32];
@@ -769,8 +779,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int pair = p.sorted[slot];
         const bool live = pair >= 0 && pair < p.num_pairs;
         const float w = live ? p.topk_weights[pair] : 0.f;
-        __nv_bfloat16* dst = p.out + static_cast<long long>(live ? pair : 0) * p.out_ld +
-                             static_cast<long long>(c.n_tile) * kBlockN;
+        // With an output table the row goes straight to the GPU that owns the token (a plain
+        // store through a peer mapping): the return all-to-all is this epilogue.
+        __nv_bfloat16* base = p.out;
+        long long out_row = live ? pair : 0;
+        if (p.out_table != nullptr && live) {
+          const long long owner = out_row / p.pairs_per_rank;
+          base = p.out_table[owner];
+          out_row -= owner * p.pairs_per_rank;
+        }
+        __nv_bfloat16* dst = base + out_row * p.out_ld + static_cast<long long>(c.n_tile) * kBlockN;
 #pragma unroll 1
         for (int ch = 0; ch < kBlockN / 32; ++ch) {
           uint32_t v[32];
@@ -1047,6 +1065,54 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   p.out = static_cast<__nv_bfloat16*>(out);
   p.capacity = sorted_capacity;
   p.num_pairs = num_pairs;
+  p.num_experts = num_experts;
+  p.k_blocks = static_cast<int>(inter / kBlockK);
+  p.n_tiles = static_cast<int>(hidden / kBlockN);
+  p.b_rows_per_expert = static_cast<int>(hidden);
+  p.inter = 0;
+  p.out_ld = hidden;
+  set_width(&p, kBlockN);
+  if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_grouped_gemm_w2_scale_peer(
+    const void* act, const void* w2, void* const* out_table, int num_ranks, int64_t pairs_per_rank,
+    const float* topk_weights, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+    const int32_t* num_tokens_post_pad, int64_t sorted_capacity, int num_experts, int64_t hidden,
+    int64_t inter, int block_m, b200moe_stream_t stream) {
+  using namespace b200moe;
+  const char* name = "grouped_gemm_w2_scale_peer";
+  if (int rc = check_common(name, num_experts, hidden, inter, block_m, sorted_capacity)) return rc;
+  if (inter % kBlockK != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: intermediate size %lld must be a multiple of %d", name,
+                (long long)inter, kBlockK);
+  if (hidden % kBlockN != 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld must be a multiple of %d", name, (long long)hidden, kBlockN);
+  if (num_ranks < 1 || pairs_per_rank < 1 || num_ranks * pairs_per_rank > 0x7fffffffLL)
+    return fail(B200MOE_ERR_SHAPE, "%s: num_ranks=%d pairs_per_rank=%lld", name, num_ranks,
+                (long long)pairs_per_rank);
+  if (sorted_capacity < block_m) return B200MOE_OK;
+  if (!act || !w2 || !out_table || !topk_weights || !sorted_token_ids || !expert_ids ||
+      !num_tokens_post_pad)
+    return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
+  if (!aligned_to(act, 16) || !aligned_to(w2, 16))
+    return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
+  if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter,
+                         block_m == kPairBlockM ? kBlockN / 2 : kBlockN, name))
+    return rc;
+  GemmParams p{};
+  p.expert_ids = expert_ids;
+  p.npp = num_tokens_post_pad;
+  p.sorted = sorted_token_ids;
+  p.topk_weights = topk_weights;
+  p.out = nullptr;
+  p.out_table = reinterpret_cast<__nv_bfloat16* const*>(out_table);
+  p.pairs_per_rank = pairs_per_rank;
+  p.capacity = sorted_capacity;
+  p.num_pairs = static_cast<long long>(num_ranks) * pairs_per_rank;
   p.num_experts = num_experts;
   p.k_blocks = static_cast<int>(inter / kBlockK);
   p.n_tiles = static_cast<int>(hidden / kBlockN);

@@ -17,6 +17,17 @@ Rows always land in the receiving GPU's own memory (NCCL receive buffers) before
 touches them.  Every arithmetic step is the one the single-GPU layer performs on the same row, so
 the result is bit-identical to the single-GPU result for the same tokens.
 
+That exchange needs the split sizes on the host, i.e. one device synchronisation per call.  When
+every rank holds the same number of tokens, ``ExpertParallelMoE`` instead moves the rows inside
+its own kernels over NVLink peer mappings and never synchronises with the host:
+
+    route locally -> copy the tokens into a peer-visible staging buffer
+    -> all-gather the (tiny) expert ids and routing weights
+    -> align the global ids against the local experts (ids of other ranks' experts are skipped)
+    -> gather_rows_peer: PULL the routed rows from their owners' staging buffers
+    -> grouped GEMM 1 -> grouped GEMM 2 whose epilogue STORES every output row into the owner's
+       [T_local, top_k, H] buffer -> one-word all-reduce (every rank's stores are done) -> combine
+
 The exchange logic is written against a small ``ops`` object so that it can be exercised on CPU
 ranks (gloo) in tests with a stand-in ``ops``; the product default is :class:`CudaOps` and nothing
 in this package implements the arithmetic on the CPU.
@@ -31,6 +42,54 @@ import torch.nn as nn
 
 from . import _C, _lib
 from .layers.moe.fused_moe import BLOCK_SIZE_M, _timed
+
+
+class _RawDeviceMemory:
+    """Adapter that lets torch view a raw device allocation."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class PeerBuffer:
+    """A device buffer that every rank of ``group`` (all on one node) can address: a cudaMalloc
+    allocation per rank, shared with CUDA IPC handles.  ``table`` is a device int64 tensor holding
+    the address of every rank's buffer as seen from this process (own buffer: the local address);
+    ``local`` is a uint8 torch view of the own buffer.  Creating one is a set-up step (it
+    allocates, synchronises and exchanges handles through the process group)."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None):
+        import ctypes
+        lib = _lib.load()
+        self._lib = lib
+        self.nbytes = nbytes
+        self.rank = dist.get_rank(group)
+        world = dist.get_world_size(group)
+        own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            _lib.check(lib.b200moe_peer_alloc(nbytes, ctypes.byref(own), handle), "peer_alloc")
+            handles = [None] * world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.ptrs = []
+            for r in range(world):
+                if r == self.rank:
+                    self.ptrs.append(own.value)
+                else:
+                    mapped = ctypes.c_void_p()
+                    buf = ctypes.create_string_buffer(handles[r], 64)
+                    _lib.check(lib.b200moe_peer_open(buf, ctypes.byref(mapped)), "peer_open")
+                    self.ptrs.append(mapped.value)
+        self.table = torch.tensor(self.ptrs, dtype=torch.int64, device=device)
+        self.local = torch.as_tensor(_RawDeviceMemory(own.value, nbytes), device=device)
+
+    def close(self) -> None:
+        for r, ptr in enumerate(self.ptrs):
+            if r != self.rank:
+                self._lib.b200moe_peer_close(ptr)
+        self._lib.b200moe_peer_free(self.ptrs[self.rank])
+        self.ptrs = []
 
 
 class CudaOps:
@@ -152,8 +211,13 @@ class ExpertParallelMoE(nn.Module):
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
                  params_dtype: Optional[torch.dtype] = None, renormalize: bool = True,
-                 group: Optional[dist.ProcessGroup] = None, ops=None):
+                 group: Optional[dist.ProcessGroup] = None, ops=None,
+                 exchange: str = "auto"):
         super().__init__()
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError("exchange must be 'auto', 'peer' or 'nccl'")
+        self.exchange = exchange
+        self._peer_states = {}
         self.group = group
         self.ep_size = dist.get_world_size(group)
         self.ep_rank = dist.get_rank(group)
@@ -200,7 +264,90 @@ class ExpertParallelMoE(nn.Module):
         dist.all_to_all_single(recv, send.contiguous(), recv_splits, send_splits, group=self.group)
         return recv
 
+    # ------------------------------------------------------------------ peer-memory exchange
+    def _peer_state(self, num_tokens: int, hidden: int, device: torch.device):
+        """Buffers of the peer-memory path for batches of ``num_tokens`` tokens per rank, or None
+        when the ranks do not all hold that many tokens (set-up: allocates and synchronises)."""
+        key = (num_tokens, hidden, device)
+        if key in self._peer_states:
+            return self._peer_states[key]
+        counts = [None] * self.ep_size
+        dist.all_gather_object(counts, num_tokens, group=self.group)
+        state = None
+        if all(c == num_tokens for c in counts) and num_tokens > 0:
+            ep, k, per = self.ep_size, self.top_k, self.experts_per_rank
+            pairs_total = ep * num_tokens * k
+            cap = pairs_total + per * (BLOCK_SIZE_M - 1)
+            i32 = dict(dtype=torch.int32, device=device)
+            bf16 = dict(dtype=torch.bfloat16, device=device)
+            x_stage = PeerBuffer(num_tokens * hidden * 2, device, self.group)
+            cache3 = PeerBuffer(num_tokens * k * hidden * 2, device, self.group)
+            state = {
+                "x_stage": x_stage, "cache3": cache3, "capacity": cap,
+                "x_local": x_stage.local.view(torch.bfloat16).view(num_tokens, hidden),
+                "c3_local": cache3.local.view(torch.bfloat16).view(num_tokens, k, hidden),
+                "ids_all": torch.empty(pairs_total, **i32),
+                "w_all": torch.empty(pairs_total, dtype=torch.float32, device=device),
+                "sorted_ids": torch.empty(cap, **i32),
+                "expert_ids": torch.zeros((cap + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M, **i32),
+                "num_post_pad": torch.zeros(1, **i32),
+                "align_ws": torch.empty(max(_C.align_workspace_numel(pairs_total, per), 1), **i32),
+                "a_sorted": torch.empty(cap, hidden, **bf16),
+                "act": torch.empty(cap, self.intermediate_size, **bf16),
+                "token": torch.zeros(1, **i32),
+            }
+        self._peer_states[key] = state
+        return state
+
+    def _forward_peer(self, st: dict, hidden_states: torch.Tensor,
+                      router_logits: torch.Tensor) -> torch.Tensor:
+        lib = _lib.load()
+        ep, per, k = self.ep_size, self.experts_per_rank, self.top_k
+        num_tokens, hidden = hidden_states.shape
+        dev = hidden_states.device
+        cap = st["capacity"]
+        weights, ids = self.ops.route(router_logits, k, self.renormalize)
+        st["x_local"].copy_(hidden_states)
+        # The all-gathers also order every rank's staging copy before any rank's gather.
+        dist.all_gather_into_tensor(st["ids_all"], ids.view(-1), group=self.group)
+        dist.all_gather_into_tensor(st["w_all"], weights.view(-1), group=self.group)
+        local_ids = st["ids_all"] - self.first_expert  # other ranks' experts fall outside [0, per)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        with _timed("moe_align_block_size"):
+            _C.moe_align_block_size(local_ids, per, BLOCK_SIZE_M, st["sorted_ids"], st["expert_ids"],
+                                    st["num_post_pad"], fill_pads=True, workspace=st["align_ws"])
+        with _timed("gather_rows"):
+            _lib.check(lib.b200moe_gather_rows_peer(
+                st["x_stage"].table.data_ptr(), ep, num_tokens, st["a_sorted"].data_ptr(),
+                st["sorted_ids"].data_ptr(), st["num_post_pad"].data_ptr(), cap, hidden, k, stream),
+                "gather_rows_peer")
+        with _timed("grouped_gemm_w13_swiglu"):
+            _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(
+                st["a_sorted"].data_ptr(), self.w13_weight.data_ptr(), st["act"].data_ptr(),
+                st["expert_ids"].data_ptr(), st["num_post_pad"].data_ptr(), cap, per, hidden,
+                self.intermediate_size, BLOCK_SIZE_M, stream), "grouped_gemm_w13_swiglu")
+        with _timed("grouped_gemm_w2_scale"):
+            _lib.check(lib.b200moe_grouped_gemm_w2_scale_peer(
+                st["act"].data_ptr(), self.w2_weight.data_ptr(), st["cache3"].table.data_ptr(), ep,
+                num_tokens * k, st["w_all"].data_ptr(), st["sorted_ids"].data_ptr(),
+                st["expert_ids"].data_ptr(), st["num_post_pad"].data_ptr(), cap, per, hidden,
+                self.intermediate_size, BLOCK_SIZE_M, stream), "grouped_gemm_w2_scale_peer")
+        _lib.count_launches(3)
+        # Every rank's second GEMM (whose epilogue wrote into this rank's buffer) has finished once
+        # this one-word all-reduce completes.
+        dist.all_reduce(st["token"], group=self.group)
+        with _timed("moe_sum"):
+            _C.moe_sum(st["c3_local"], hidden_states)
+        return hidden_states
+
     def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        if self.exchange != "nccl" and isinstance(self.ops, CudaOps):
+            st = self._peer_state(hidden_states.shape[0], hidden_states.shape[1],
+                                  hidden_states.device)
+            if st is not None:
+                return self._forward_peer(st, hidden_states, router_logits)
+            if self.exchange == "peer":
+                raise RuntimeError("exchange='peer' needs the same token count on every rank")
         ops, ep, per = self.ops, self.ep_size, self.experts_per_rank
         dev = hidden_states.device
         weights, ids = ops.route(router_logits, self.top_k, self.renormalize)

@@ -4,7 +4,8 @@
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream, launches
  * asynchronously on that stream, never synchronises, never allocates device memory and never
- * throws.  The return value is 0 on success or a negative B200MOE_ERR_* code; the text of the
+ * throws (the b200moe_peer_* set-up helpers and b200moe_gemm_device_status are the exceptions and
+ * say so).  The return value is 0 on success or a negative B200MOE_ERR_* code; the text of the
  * most recent failure on the calling thread is available from b200moe_last_error().
  *
  * Each declaration names the reference interface it replaces (paths are relative to the
@@ -245,6 +246,46 @@ int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, void* out,
                                   int64_t sorted_capacity, int64_t num_pairs, int num_experts,
                                   int64_t hidden, int64_t inter, int block_m,
                                   b200moe_stream_t stream);
+
+/*
+ * Expert-parallel variants that move rows over NVLink inside the kernels themselves (no reference
+ * counterpart: the reference has no expert parallelism, layers/moe/mixtral_moe.py:9-13).
+ *
+ * b200moe_gather_rows_peer is b200moe_gather_rows with the token tensor split over num_ranks GPUs:
+ * token row r is row r % rows_per_rank of the tensor at src_table[r / rows_per_rank].  src_table is a
+ * DEVICE array of num_ranks device pointers (local memory or peer mappings); the kernel pulls the
+ * rows with plain loads.  This is the dispatch step.
+ *
+ * b200moe_grouped_gemm_w2_scale_peer is b200moe_grouped_gemm_w2_scale whose epilogue stores output
+ * row p (a global pair index) to row p % pairs_per_rank of the tensor at
+ * out_table[p / pairs_per_rank] (a DEVICE array of device pointers), i.e. directly into the memory
+ * of the GPU that owns the token.  This is the return step.  topk_weights holds num_ranks *
+ * pairs_per_rank entries (the routing weights of all ranks).  The caller orders the ranks around
+ * these kernels (every rank's source rows must be in place before any rank gathers; every rank's
+ * second GEMM must have finished before a rank combines) with stream-ordered collectives.
+ */
+int b200moe_gather_rows_peer(const void* const* src_table, int num_ranks, int64_t rows_per_rank,
+                             void* dst, const int32_t* sorted_token_ids,
+                             const int32_t* num_tokens_post_pad, int64_t sorted_capacity,
+                             int64_t row_elems, int top_k, b200moe_stream_t stream);
+int b200moe_grouped_gemm_w2_scale_peer(const void* act, const void* w2, void* const* out_table,
+                                       int num_ranks, int64_t pairs_per_rank,
+                                       const float* topk_weights, const int32_t* sorted_token_ids,
+                                       const int32_t* expert_ids,
+                                       const int32_t* num_tokens_post_pad, int64_t sorted_capacity,
+                                       int num_experts, int64_t hidden, int64_t inter, int block_m,
+                                       b200moe_stream_t stream);
+
+/*
+ * Set-up helpers for peer-visible buffers (these DO allocate and synchronise; not for the hot
+ * path).  b200moe_peer_alloc: cudaMalloc + zero fill + CUDA IPC handle (64 bytes) for the other
+ * rank processes of the node.  b200moe_peer_open maps another process's buffer from its handle;
+ * b200moe_peer_close unmaps it; b200moe_peer_free releases an own buffer.
+ */
+int b200moe_peer_alloc(size_t bytes, void** ptr, void* ipc_handle_64);
+int b200moe_peer_open(const void* ipc_handle_64, void** ptr);
+int b200moe_peer_close(void* ptr);
+int b200moe_peer_free(void* ptr);
 
 /*
  * Device-side status word of the grouped GEMMs.  Their waits on memory barriers are bounded; a

@@ -42,7 +42,7 @@ def _worker(rank, port, mode, result_dir):
     single = fused_experts(full["x"].to(dev), full["w13"].to(dev), full["w2"].to(dev),
                            full["logits"].to(dev), 2, inplace=False)
     res = {}
-    if mode == "tp":
+    if mode == "tp":  # noqa: SIM102
         layer = FusedMoE(8, 2, wl.hidden, wl.inter, tp_size=WORLD, params_dtype=torch.bfloat16,
                          reduce_results=True).to(dev)
         for e in range(8):
@@ -56,24 +56,33 @@ def _worker(rank, port, mode, result_dir):
         res["stats"] = moe_oracle.error_stats(out.cpu().float(), want)
         res["vs_single"] = moe_oracle.error_stats(out.cpu().float(), single.cpu().float())
     else:
-        layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16).to(dev)
+        layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
+                                  exchange="peer" if mode == "ep_peer" else "nccl").to(dev)
         for e in range(8):
             layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
             layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
             layer.weight_loader(layer.w2_weight, full["w2"][e].to(dev), "w2", e)
-        lo, hi = (0, 350) if rank == 0 else (350, 600)  # uneven token split
+        if mode == "ep_peer":
+            lo, hi = (0, 300) if rank == 0 else (300, 600)  # the peer-memory exchange needs equal splits
+        else:
+            lo, hi = (0, 350) if rank == 0 else (350, 600)  # uneven token split
         x = full["x"][lo:hi].to(dev).clone()
         out = layer(x, full["logits"][lo:hi].to(dev))
         torch.cuda.synchronize()
         res["alias"] = out.data_ptr() == x.data_ptr()
         res["stats"] = moe_oracle.error_stats(out.cpu().float(), want[lo:hi])
         res["bit_exact_vs_single"] = bool(torch.equal(out, single[lo:hi]))
+        # Second call on the same buffers (staging and return buffers are reused every step).
+        x2 = full["x"][lo:hi].to(dev).flip(0).contiguous()
+        out2 = layer(x2, full["logits"][lo:hi].to(dev).flip(0).contiguous())
+        torch.cuda.synchronize()
+        res["bit_exact_second_call"] = bool(torch.equal(out2, single[lo:hi].flip(0)))
     res["gemm_status"] = _lib.load().b200moe_gemm_device_status(1)
     torch.save(res, os.path.join(result_dir, f"{mode}{rank}.pt"))
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["tp", "ep"])
+@pytest.mark.parametrize("mode", ["tp", "ep", "ep_peer"])
 def test_two_gpu_layer(tmp_path, mode):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
@@ -82,8 +91,9 @@ def test_two_gpu_layer(tmp_path, mode):
         r = torch.load(tmp_path / f"{mode}{rank}.pt")
         assert r["alias"] and r["gemm_status"] == 0, r
         assert r["stats"]["max_abs"] <= 3e-2 and r["stats"]["rel_fro"] <= 1e-2, r
-        if mode == "ep":
+        if mode.startswith("ep"):
             assert r["bit_exact_vs_single"], "expert-parallel rows must equal the single-GPU rows"
+            assert r["bit_exact_second_call"]
         else:
             # TP sums two bf16-rounded partial outputs: close to, not identical with, one GPU.
             assert r["vs_single"]["rel_fro"] <= 1e-2, r
