@@ -128,6 +128,54 @@ def test_grouped_gemm_w13_gather_matches_pregathered_rows(T, H, I, E, k):
     assert (act1[used:] == 9.0).all()
 
 
+def test_peer_table_kernels_on_one_gpu():
+    """The expert-parallel kernels address their source rows and output rows through a table of
+    per-rank base pointers.  With two local buffers standing in for two ranks, the pull-gather and
+    the table-driven epilogue must reproduce the single-buffer kernels bit for bit."""
+    lib = _lib.load()
+    ranks, T_loc, H, I, E, k = 2, 150, 512, 256, 4, 2
+    T = ranks * T_loc
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).to(torch.bfloat16).to(DEV)
+    w2 = (torch.randn(E, H, I, generator=g) / I ** 0.5).to(torch.bfloat16).to(DEV)
+    tw = torch.rand(T * k, generator=g).to(DEV)
+    # Global expert ids over 8 experts; this "rank" owns experts 4..7, the others are skipped.
+    ids = torch.randint(0, 8, (T * k,), generator=g, dtype=torch.int32) - 4
+    s, e, n = aligned(ids.numpy(), E)
+    cap = s.size
+    d_s, d_e, d_n = torch.from_numpy(s).to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    halves = [x[:T_loc].clone(), x[T_loc:].clone()]
+    src_table = torch.tensor([h.data_ptr() for h in halves], dtype=torch.int64, device=DEV)
+    a0 = torch.empty(cap, H, dtype=torch.bfloat16, device=DEV)
+    a1 = torch.empty(cap, H, dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.b200moe_gather_rows(x.data_ptr(), a0.data_ptr(), d_s.data_ptr(), d_n.data_ptr(),
+                                       cap, T, H, k, stream), "gather_rows")
+    _lib.check(lib.b200moe_gather_rows_peer(src_table.data_ptr(), ranks, T_loc, a1.data_ptr(),
+                                            d_s.data_ptr(), d_n.data_ptr(), cap, H, k, stream),
+               "gather_rows_peer")
+    used = int(n[0])
+    assert torch.equal(a0[:used], a1[:used])
+    act = torch.empty(cap, I, dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(a1.data_ptr(), w13.data_ptr(), act.data_ptr(),
+                                                   d_e.data_ptr(), d_n.data_ptr(), cap, E, H, I, 128,
+                                                   stream), "w13")
+    out0 = torch.full((T * k, H), 5.0, dtype=torch.bfloat16, device=DEV)
+    outs = [torch.full((T_loc * k, H), 5.0, dtype=torch.bfloat16, device=DEV) for _ in range(ranks)]
+    out_table = torch.tensor([o.data_ptr() for o in outs], dtype=torch.int64, device=DEV)
+    _lib.check(lib.b200moe_grouped_gemm_w2_scale(
+        act.data_ptr(), w2.data_ptr(), out0.data_ptr(), tw.data_ptr(), d_s.data_ptr(), d_e.data_ptr(),
+        d_n.data_ptr(), cap, T * k, E, H, I, 128, stream), "w2")
+    _lib.check(lib.b200moe_grouped_gemm_w2_scale_peer(
+        act.data_ptr(), w2.data_ptr(), out_table.data_ptr(), ranks, T_loc * k, tw.data_ptr(),
+        d_s.data_ptr(), d_e.data_ptr(), d_n.data_ptr(), cap, E, H, I, 128, stream), "w2 peer")
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    assert torch.equal(out0, torch.cat(outs))   # rows of skipped pairs keep the 5.0 fill in both
+    assert (out0 == 5.0).all(dim=1).sum().item() == int((ids < 0).sum() + (ids >= E).sum())
+
+
 # --------------------------------------------------------------------------------- whole layer
 def run_layer(inp, wl, inplace=True):
     x = inp["x"].to(torch.bfloat16).to(DEV).clone()
