@@ -66,6 +66,46 @@ def topk_softmax(topk_weights: torch.Tensor, topk_indices: torch.Tensor,
     _lib.count_launches(1 if num_tokens else 0)
 
 
+def gate_topk_softmax(topk_weights: torch.Tensor, topk_indices: torch.Tensor,
+                      hidden_states: torch.Tensor, gate_weight: torch.Tensor,
+                      renormalize: bool = False, logits_out: torch.Tensor | None = None,
+                      round_logits_bf16: bool = True) -> None:
+    """Gate projection + softmax + top-2 in one kernel (no counterpart among the reference's ops:
+    it replaces the gate ``F.linear`` of models/mixtral.py:59 followed by the router).
+
+    ``hidden_states`` bf16 ``[T, H]``, ``gate_weight`` bf16 ``[8, H]``; ``topk_weights`` f32
+    ``[T, 2]`` and ``topk_indices`` i32 ``[T, 2]`` are overwritten; ``logits_out`` (f32 ``[T, 8]``)
+    optionally receives the logits.  ``round_logits_bf16`` rounds the fp32-accumulated logits to
+    bf16 before routing, which is what the reference's bf16 gate layer produces.
+    """
+    name = "gate_topk_softmax"
+    tensors = [topk_weights, topk_indices, hidden_states, gate_weight]
+    if logits_out is not None:
+        tensors.append(logits_out)
+    dev = _require_cuda(name, *tensors)
+    if hidden_states.dtype != torch.bfloat16 or gate_weight.dtype != torch.bfloat16:
+        raise RuntimeError(f"{name}: hidden_states and gate_weight must be bfloat16")
+    if topk_weights.dtype != torch.float32 or topk_indices.dtype != torch.int32:
+        raise RuntimeError(f"{name}: topk_weights must be float32 and topk_indices int32")
+    if hidden_states.dim() != 2 or gate_weight.dim() != 2 or gate_weight.size(1) != hidden_states.size(1):
+        raise RuntimeError(f"{name}: expected hidden_states [T, H] and gate_weight [E, H]")
+    num_tokens, hidden = hidden_states.shape
+    num_experts, topk = gate_weight.size(0), topk_weights.size(-1)
+    if topk_weights.numel() != num_tokens * topk or topk_indices.numel() != num_tokens * topk:
+        raise RuntimeError(f"{name}: outputs must hold num_tokens * topk elements")
+    if logits_out is not None and (logits_out.dtype != torch.float32
+                                   or logits_out.numel() != num_tokens * num_experts):
+        raise RuntimeError(f"{name}: logits_out must be float32 [num_tokens, num_experts]")
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200moe_gate_topk_softmax(
+            hidden_states.data_ptr(), gate_weight.data_ptr(), topk_weights.data_ptr(),
+            topk_indices.data_ptr(), logits_out.data_ptr() if logits_out is not None else None,
+            num_tokens, hidden, num_experts, topk, int(renormalize), int(round_logits_bf16),
+            _stream(dev))
+    _lib.check(rc, name)
+    _lib.count_launches(1 if num_tokens else 0)
+
+
 def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: int,
                          sorted_token_ids: torch.Tensor, expert_ids: torch.Tensor,
                          num_tokens_post_pad: torch.Tensor,

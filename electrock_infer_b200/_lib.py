@@ -21,6 +21,8 @@ SIGNATURES = {
     "b200moe_last_error": (c_char_p, []),
     "b200moe_topk_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
                                      c_int, c_void_p]),
+    "b200moe_gate_topk_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                          c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200moe_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64,
                                          c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                                          c_size_t, c_void_p]),

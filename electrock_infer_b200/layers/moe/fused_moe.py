@@ -12,7 +12,7 @@ and three for long ones):
 """
 from __future__ import annotations
 
-from typing import Dict, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -130,14 +130,18 @@ class _timed:
 
 
 def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
-                  gating_output: torch.Tensor, topk: int, renormalize: bool = True,
-                  inplace: bool = False, activation: str = "silu") -> torch.Tensor:
+                  gating_output: Optional[torch.Tensor], topk: int, renormalize: bool = True,
+                  inplace: bool = False, activation: str = "silu",
+                  gate_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Mixture-of-experts forward for ``hidden_states [T, H]`` (reference fused_moe.py:170-293).
 
     ``w1`` is the stacked gate/up weight ``[E, 2*I, H]`` (gate rows first), ``w2`` is
     ``[E, H, I]``, ``gating_output`` the router logits ``[T, E]`` in any float dtype.  With
     ``inplace`` the result overwrites and aliases ``hidden_states``, as the layer relies on.
     Tensors must be bf16 on a CUDA device: there is no other implementation behind this call.
+
+    Extension: with ``gate_weight`` (bf16 ``[E, H]``) the gate projection is computed by the router
+    kernel itself and ``gating_output`` may be ``None``.
     """
     if activation != "silu":
         raise NotImplementedError(f"Activation {activation} not supported.")
@@ -152,8 +156,11 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
     if w1_k != hidden or tuple(w2.shape) != (num_experts, hidden, inter):
         raise RuntimeError(f"fused_experts: weight shapes {tuple(w1.shape)} / {tuple(w2.shape)} "
                            f"do not match hidden={hidden}")
-    if gating_output.shape != (num_tokens, num_experts):
-        raise RuntimeError("fused_experts: gating_output must be [num_tokens, num_experts]")
+    if gate_weight is None:
+        if gating_output is None or gating_output.shape != (num_tokens, num_experts):
+            raise RuntimeError("fused_experts: gating_output must be [num_tokens, num_experts]")
+    elif tuple(gate_weight.shape) != (num_experts, hidden) or not gate_weight.is_contiguous():
+        raise RuntimeError("fused_experts: gate_weight must be a contiguous [num_experts, hidden] tensor")
     for t in (hidden_states, w1, w2):
         if not t.is_contiguous():
             raise RuntimeError("fused_experts: hidden_states, w1 and w2 must be contiguous")
@@ -167,12 +174,19 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
     block_m = choose_block_m(num_tokens, topk, num_experts)
     ws = _workspace.get(dev, num_tokens, topk, num_experts, hidden, inter, block_m)
     capacity = ws["capacity"]
-    gating = gating_output if gating_output.is_contiguous() else gating_output.contiguous()
+    gating = None
+    if gate_weight is None:
+        gating = gating_output if gating_output.is_contiguous() else gating_output.contiguous()
 
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
-        with _timed("topk_softmax"):
-            _C.topk_softmax(ws["topk_weights"], ws["topk_ids"], gating, renormalize=renormalize)
+        if gate_weight is None:
+            with _timed("topk_softmax"):
+                _C.topk_softmax(ws["topk_weights"], ws["topk_ids"], gating, renormalize=renormalize)
+        else:
+            with _timed("gate_topk_softmax"):
+                _C.gate_topk_softmax(ws["topk_weights"], ws["topk_ids"], hidden_states, gate_weight,
+                                     renormalize=renormalize)
         with _timed("moe_align_block_size"):
             _C.moe_align_block_size(ws["topk_ids"], num_experts, block_m, ws["sorted_ids"],
                                     ws["expert_ids"], ws["num_post_pad"], fill_pads=True,

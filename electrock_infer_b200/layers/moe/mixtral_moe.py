@@ -84,3 +84,48 @@ class FusedMoE(nn.Module):
             param_data.copy_(loaded)
         else:
             raise ValueError(f"unknown shard_id: {shard_id}")
+
+
+class MixtralMoE(nn.Module):
+    """Gate + experts, the block the reference's decoder layer calls (models/mixtral.py:21-63):
+    ``gate`` is a replicated bias-free linear layer ``[hidden -> num_experts]`` (its parameter is
+    ``gate.weight`` with the loader signature of layers/linear.py:47-49) and ``experts`` is a
+    ``FusedMoE`` with ``reduce_results=True, renormalize=True``.
+
+    ``forward(hidden_states)`` accepts 1-D or 2-D token shapes, overwrites the tokens with the
+    layer output and returns them in the original shape, like the reference.  Unlike the
+    reference, the gate projection is not a separate GEMM: the router kernel computes it while it
+    reads the tokens.  ``fuse_gate=False`` restores the separate ``F.linear``.
+    """
+
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
+                 params_dtype: Optional[torch.dtype] = None, tp_size: Optional[int] = None,
+                 prefix: str = "", fuse_gate: bool = True):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.fuse_gate = fuse_gate
+        self.gate = nn.Linear(hidden_size, num_experts, bias=False,
+                              dtype=params_dtype or torch.get_default_dtype())
+        self.gate.weight.requires_grad_(False)
+        self.gate.weight.weight_loader = self._gate_weight_loader
+        self.experts = FusedMoE(num_experts=num_experts, top_k=top_k, hidden_size=hidden_size,
+                                intermediate_size=intermediate_size, params_dtype=params_dtype,
+                                reduce_results=True, renormalize=True, tp_size=tp_size)
+
+    @staticmethod
+    def _gate_weight_loader(param: nn.Parameter, loaded_weight: torch.Tensor) -> None:
+        assert param.size() == loaded_weight.size()
+        param.data.copy_(loaded_weight)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        orig_shape = hidden_states.shape
+        hidden_states = hidden_states.view(-1, self.hidden_size)
+        if self.fuse_gate:
+            out = fused_experts(hidden_states, self.experts.w13_weight, self.experts.w2_weight, None,
+                                self.experts.top_k, renormalize=True, inplace=True,
+                                gate_weight=self.gate.weight)
+            if self.experts.tp_size > 1:
+                dist.all_reduce(out)
+        else:
+            out = self.experts(hidden_states, self.gate(hidden_states))
+        return out.view(orig_shape)

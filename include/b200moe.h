@@ -79,6 +79,23 @@ int b200moe_topk_softmax(float* topk_weights, int32_t* topk_indices, const void*
                          int renormalize, b200moe_stream_t stream);
 
 /*
+ * Gate projection fused with the router: logits[t, e] = sum_h hidden_states[t, h] * gate_weight[e, h]
+ * (fp32 accumulation of bf16 inputs), then the softmax + top-2 of b200moe_topk_softmax, in one pass
+ * over the activations.  Replaces the gate linear layer plus the router call of the reference's
+ * MixtralMoE.forward (models/mixtral.py:59-61: ReplicatedLinear, layers/linear.py:32-54, followed
+ * by fused_topk, layers/moe/fused_moe.py:130-164).
+ *
+ *   hidden_states bf16 [num_tokens, hidden], gate_weight bf16 [8, hidden]; hidden % 256 == 0 and
+ *   8 * hidden * 2 bytes must fit in shared memory (hidden <= 12800)
+ *   logits_out    optional f32 [num_tokens, 8]: the logits the routing decision was made on
+ *   round_logits_bf16 != 0 rounds the logits to bf16 first, like the reference's bf16 linear layer
+ */
+int b200moe_gate_topk_softmax(const void* hidden_states, const void* gate_weight,
+                              float* topk_weights, int32_t* topk_indices, float* logits_out,
+                              int64_t num_tokens, int64_t hidden, int num_experts, int topk,
+                              int renormalize, int round_logits_bf16, b200moe_stream_t stream);
+
+/*
  * Token alignment: counting sort of the flat (token, slot) pairs by expert, each expert's run
  * padded to a multiple of block_size.  Replaces electrock_infer::moe_align_block_size
  * (src/moe_align_block_size.cu:140-230, bound in pytorch_bind.cpp:43-50).

@@ -71,6 +71,14 @@ def router_ref(logits: torch.Tensor, topk: int = 2,
     return weights, order.to(torch.int32)
 
 
+def gate_logits_ref(x: torch.Tensor, gate_w: torch.Tensor, round_bf16: bool = True) -> torch.Tensor:
+    """Router logits of the reference block: ``gate(hidden_states)`` with a bias-free linear layer
+    (models/mixtral.py:59; layers/linear.py:53-54).  Computed in fp32 from the stored values; the
+    reference's bf16 layer returns them rounded to bf16 (``round_bf16``)."""
+    logits = x.detach().cpu().float() @ gate_w.detach().cpu().float().T
+    return logits.to(torch.bfloat16).float() if round_bf16 else logits
+
+
 def tie_rows(logits: torch.Tensor, topk: int = 2) -> torch.Tensor:
     """Boolean mask of rows where the top-k *set or order* is decided by an exact tie, i.e. where
     two implementations with different tie rules may legitimately disagree."""
