@@ -224,3 +224,33 @@ def moe_sum_efficient(input: torch.Tensor, output: torch.Tensor) -> None:  # noq
     """Same sum for the interleaved layout ``input [T, H, 2]``
     (src/moe_sum_efficient.cu:52-79); bf16 is accepted in addition to fp32/fp16."""
     _moe_sum("moe_sum_efficient", input, output, 1)
+
+
+def _rms_norm(name: str, input: torch.Tensor, residual, epsilon: float,  # noqa: A002
+              weight: torch.Tensor) -> None:
+    tensors = [input, weight] + ([residual] if residual is not None else [])
+    dev = _require_cuda(name, *tensors)
+    if input.dim() != 2 or weight.dim() != 1 or weight.numel() != input.size(1):
+        raise RuntimeError(f"{name}: expected input [num_tokens, hidden] and weight [hidden]")
+    if weight.dtype != input.dtype or (residual is not None and (
+            residual.dtype != input.dtype or residual.shape != input.shape)):
+        raise RuntimeError(f"{name}: input, residual and weight must share dtype and shape")
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200moe_add_rms_norm(
+            input.data_ptr(), residual.data_ptr() if residual is not None else None,
+            weight.data_ptr(), _float_tag(name, input), input.size(0), input.size(1),
+            float(epsilon), _stream(dev))
+    _lib.check(rc, name)
+    _lib.count_launches(1 if input.numel() else 0)
+
+
+def rms_norm(input: torch.Tensor, epsilon: float, weight: torch.Tensor) -> None:  # noqa: A002
+    """In-place RMSNorm of every row (reference op: pytorch_bind.cpp:53-58)."""
+    _rms_norm("rms_norm", input, None, epsilon, weight)
+
+
+def add_rms_norm(input: torch.Tensor, residual: torch.Tensor, epsilon: float,  # noqa: A002
+                 weight: torch.Tensor) -> None:
+    """``residual <- input + residual`` then ``input <- RMSNorm(residual) * weight``, both in place
+    (reference op: pytorch_bind.cpp:60-66; arithmetic of layers/layernorm.py:30-43)."""
+    _rms_norm("add_rms_norm", input, residual, epsilon, weight)

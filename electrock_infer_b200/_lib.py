@@ -36,6 +36,8 @@ SIGNATURES = {
     "b200moe_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p]),
     "b200moe_moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int,
                                 c_void_p]),
+    "b200moe_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
+                                     ctypes.c_float, c_void_p]),
     "b200moe_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                     c_int64, c_int, c_void_p]),
     "b200moe_scatter_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

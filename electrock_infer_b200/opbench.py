@@ -76,6 +76,17 @@ def main() -> None:
         xi = x.view(T, H, 2)
         ms = time_op(lambda: _C.moe_sum_efficient(xi, out), args.iters, flush)
         report("moe_sum_efficient", T, T * H * 2 * 3, ms)
+    for T in args.combine_tokens:
+        x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+        gw = (torch.randn(8, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        w = torch.empty(T, 2, device=dev)
+        ids = torch.empty(T, 2, dtype=torch.int32, device=dev)
+        ms = time_op(lambda: _C.gate_topk_softmax(w, ids, x, gw, renormalize=True), args.iters, flush)
+        report("gate_topk_softmax", T, T * (H * 2 + 16), ms)
+        res = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+        nw = torch.ones(H, dtype=torch.bfloat16, device=dev)
+        ms = time_op(lambda: _C.add_rms_norm(x, res, 1e-5, nw), args.iters, flush)
+        report("add_rms_norm", T, T * H * 2 * 4, ms)
     for rows, d in ((16384, 14336), (4096, 14336)):
         x = torch.randn(rows, 2 * d, generator=g, device=dev).to(torch.bfloat16)
         out = torch.empty(rows, d, dtype=torch.bfloat16, device=dev)

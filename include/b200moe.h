@@ -182,6 +182,23 @@ int b200moe_moe_sum(const void* input, void* output, int dtype, int64_t num_toke
                     int topk, int layout, b200moe_stream_t stream);
 
 /*
+ * RMSNorm of every row, optionally fused with the residual add that precedes it in the decoder
+ * layer; this is the kernel that produces the MoE layer's input.  Replaces
+ * electrock_infer::rms_norm / add_rms_norm (src/add_rms_norm.cu:145-200 and :21-142, bound in
+ * pytorch_bind.cpp:53-66) with the arithmetic of the Python path the reference really runs
+ * (layers/layernorm.py:17-43):
+ *   residual != NULL:  s = float(input) + float(residual);  residual <- cast(s)
+ *   residual == NULL:  s = float(input)
+ *   input <- cast(s * rsqrt(mean(s^2) + epsilon)) * weight        (product in the element type)
+ * input, residual [num_tokens, hidden] and weight [hidden] share the element type dtype; hidden must
+ * be a multiple of 8 (4 for fp32) and at most 16384 (8192 for fp32).  Unlike the reference kernel
+ * there is no hidden == 4096 restriction and the launch is on the caller's stream.
+ */
+int b200moe_add_rms_norm(void* input, void* residual, const void* weight, int dtype,
+                         int64_t num_tokens, int64_t hidden, float epsilon,
+                         b200moe_stream_t stream);
+
+/*
  * Row gather into expert-sorted order: dst[s, :] = src[sorted_token_ids[s] / top_k, :] for every
  * slot s < *num_tokens_post_pad holding a pair; padding slots are zero-filled.  This is the
  * A-operand addressing of the reference's grouped GEMM (layers/moe/fused_moe.py:88-91) done once

@@ -163,6 +163,22 @@ def moe_sum_efficient_ref(x: torch.Tensor) -> torch.Tensor:
     return x[..., 0] + x[..., 1]
 
 
+def rms_norm_ref(x: torch.Tensor, weight: torch.Tensor, eps: float,
+                 residual: Optional[torch.Tensor] = None):
+    """RMSNorm, optionally after a residual add, as the reference runs it
+    (layers/layernorm.py:17-43): sum and variance in fp32, normalised value cast to the element type,
+    then multiplied by the weight in the element type.  Returns ``y`` or ``(y, new_residual)``."""
+    orig = x.dtype
+    xf = x.detach().cpu().to(torch.float32)
+    new_res = None
+    if residual is not None:
+        xf = xf + residual.detach().cpu().to(torch.float32)
+        new_res = xf.to(orig)
+    var = xf.pow(2).mean(dim=-1, keepdim=True)
+    y = (xf * torch.rsqrt(var + eps)).to(orig) * weight.detach().cpu().to(orig)
+    return y if residual is None else (y, new_res)
+
+
 # ------------------------------------------------------------------------------------ the layer
 def moe_block_ref(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, logits: torch.Tensor,
                   topk: int = 2, renormalize: bool = True,
