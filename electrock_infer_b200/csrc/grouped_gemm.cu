@@ -107,9 +107,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1) {
   asm volatile(
@@ -205,12 +202,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
-// Instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
+// Instruction descriptor: D fp32, A and B bf16, both K-major, N and M as given.
 constexpr uint32_t make_instr_desc(int n, int m) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
-constexpr uint32_t kInstrDesc = make_instr_desc(kBlockN, kBlockM);
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -542,10 +538,8 @@ constexpr int kPairBBytes = (kBlockN / 2) * kBlockK * 2;    // 16384: this CTA's
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;  // 32768
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kSmemAlignSlack;
 constexpr int kPairBlockM = 2 * kBlockM;                    // rows per tile of the pair
-// Instruction descriptor: as kInstrDesc with M = 256 (128 rows in each CTA).
-constexpr uint32_t kPairInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) |
-                                    (static_cast<uint32_t>(kBlockN >> 3) << 17) |
-                                    (static_cast<uint32_t>(kPairBlockM >> 4) << 24);
+// Instruction descriptor of the pair: M = 256 (128 rows in each CTA), N = 256.
+constexpr uint32_t kPairInstrDesc = make_instr_desc(kBlockN, kPairBlockM);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
