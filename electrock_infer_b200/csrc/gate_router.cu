@@ -3,10 +3,16 @@
 //
 // In the reference the gate is a separate bf16 linear layer (ReplicatedLinear, layers/linear.py:32-54,
 // called at models/mixtral.py:59) whose [T, 8] bf16 output is fed to the router
-// (layers/moe/fused_moe.py:130-164).  Here a warp reads four token rows at a time, multiplies them
-// against the gate weight held in shared memory (each weight load is reused for the four rows),
-// reduces the 4 x 8 partial sums with shuffles and routes the four rows.  The kernel is HBM-bound
-// on the activations: 2*H bytes in per token, 16 (+32 with logits) bytes out.
+// (layers/moe/fused_moe.py:130-164).  Here a CTA owns 16 token rows and its eight warps split the
+// hidden dimension; every warp multiplies its slice with mma.sync m16n8k16 (16 tokens x 8 experts,
+// fp32 accumulate: N = 8 is exactly the expert count), the partial sums meet in shared memory and
+// 16 threads route the rows.  The kernel is HBM-bound on the activations (2*H bytes per token), so
+// the warp-level MMA is all the tensor-core work this needs.
+//
+// Operand mapping.  A lane loads 16 bytes (8 consecutive columns) of token rows g and g+8 and of
+// gate row g (g = lane / 4): a dot product does not care about the order of its terms, so the
+// lane's eight columns are fed to two MMAs as "its" k positions (2t, 2t+1, 2t+8, 2t+9 of the
+// fragment layout) for A and B alike, which keeps every global load 16 bytes wide.
 //
 // Logits are accumulated in fp32.  With round_logits_bf16 they are rounded to bf16 before the
 // softmax, which is what the reference's bf16 linear layer hands to its router; without it the
@@ -19,16 +25,16 @@ namespace {
 constexpr int kExperts = 8;
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kRowsPerWarp = 4;
-constexpr int kChunk = 32 * 8;  // columns covered by one 16-byte load per lane
+constexpr int kRowsPerCta = 16;
+constexpr int kChunk = kWarps * 32;  // hidden must split into 8 warp slices of whole 32-column steps
 
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                 uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -36,94 +42,79 @@ gate_topk_softmax_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
                          float* __restrict__ weights, int32_t* __restrict__ indices,
                          float* __restrict__ logits_out, int64_t num_tokens, int hidden,
                          int renormalize, int round_logits_bf16) {
-  extern __shared__ uint4 s_w[];  // [kExperts][hidden / 8] as 16-byte vectors
+  __shared__ float s_part[kWarps][kRowsPerCta][kExperts];
+  __shared__ float s_logit[kRowsPerCta][kExperts];
   pdl_wait();
   pdl_launch_dependents();
-  const int vec_per_row = hidden / 8;
-  for (int i = threadIdx.x; i < kExperts * vec_per_row; i += kThreads)
-    s_w[i] = __ldg(reinterpret_cast<const uint4*>(gate_w) + i);
-  __syncthreads();
-
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t groups = ceil_div64(num_tokens, kRowsPerWarp);
-  for (int64_t grp = static_cast<int64_t>(blockIdx.x) * kWarps + warp; grp < groups;
-       grp += static_cast<int64_t>(gridDim.x) * kWarps) {
-    const int64_t row0 = grp * kRowsPerWarp;
-    float acc[kRowsPerWarp][kExperts];
-#pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r)
-#pragma unroll
-      for (int e = 0; e < kExperts; ++e) acc[r][e] = 0.f;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta;
+  const bool valid0 = row0 + g < num_tokens, valid1 = row0 + g + 8 < num_tokens;
+  const __nv_bfloat16* xr0 = x + (row0 + g) * hidden;
+  const __nv_bfloat16* xr1 = x + (row0 + g + 8) * hidden;
+  const __nv_bfloat16* wr = gate_w + static_cast<int64_t>(g) * hidden;
+  const int slice = hidden / kWarps;
+  const int kbeg = warp * slice + t * 8, kend = (warp + 1) * slice;
 
-    for (int c = lane; c < vec_per_row; c += 32) {
-      float xv[kRowsPerWarp][8];
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll 4
+  for (int k = kbeg; k < kend; k += 32) {
+    const uint4 a = valid0 ? ld_stream_16(xr0 + k) : zero;
+    const uint4 b = valid1 ? ld_stream_16(xr1 + k) : zero;
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(wr + k));
+    mma_bf16_16x8x16(c, a.x, b.x, a.y, b.y, w.x, w.y);
+    mma_bf16_16x8x16(c, a.z, b.z, a.w, b.w, w.z, w.w);
+  }
+  // Accumulator layout: c0,c1 = row g, experts 2t,2t+1; c2,c3 = row g+8.
+  s_part[warp][g][2 * t] = c[0];
+  s_part[warp][g][2 * t + 1] = c[1];
+  s_part[warp][g + 8][2 * t] = c[2];
+  s_part[warp][g + 8][2 * t + 1] = c[3];
+  __syncthreads();
+  if (threadIdx.x < kRowsPerCta * kExperts) {
+    const int r = threadIdx.x / kExperts, e = threadIdx.x % kExperts;
+    float v = 0.f;
 #pragma unroll
-      for (int r = 0; r < kRowsPerWarp; ++r) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row0 + r < num_tokens)
-          v = ld_stream_16(reinterpret_cast<const uint4*>(x + (row0 + r) * hidden) + c);
-        unpack8(v, xv[r]);
-      }
-#pragma unroll
-      for (int e = 0; e < kExperts; ++e) {
-        float wv[8];
-        unpack8(s_w[e * vec_per_row + c], wv);
-#pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[r][e] = fmaf(xv[r][j], wv[j], acc[r][e]);
-      }
-    }
-    // Sum over lanes; every lane ends up with all 32 totals.
-#pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r)
-#pragma unroll
-      for (int e = 0; e < kExperts; ++e)
-#pragma unroll
-        for (int d = 16; d >= 1; d >>= 1) acc[r][e] += __shfl_xor_sync(0xffffffffu, acc[r][e], d);
-
-    // Lane r (r < 4) routes row r.  The select keeps acc in registers.
+    for (int w = 0; w < kWarps; ++w) v += s_part[w][r][e];
+    s_logit[r][e] = round_logits_bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+  }
+  __syncthreads();
+  const int64_t row = row0 + threadIdx.x;
+  if (threadIdx.x < kRowsPerCta && row < num_tokens) {
     float l[kExperts];
 #pragma unroll
-    for (int e = 0; e < kExperts; ++e) {
-      float v = acc[0][e];
+    for (int e = 0; e < kExperts; ++e) l[e] = s_logit[threadIdx.x][e];
+    // Ascending scan with strict '>' => the lower index wins a tie
+    // (src/topk_softmax_kernels.cu:39,47 of the reference).
+    float v1 = l[0], v2 = -INFINITY;
+    int i1 = 0, i2 = -1;
 #pragma unroll
-      for (int r = 1; r < kRowsPerWarp; ++r) v = (lane == r) ? acc[r][e] : v;
-      l[e] = round_logits_bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+    for (int e = 1; e < kExperts; ++e) {
+      if (l[e] > v1) { v2 = v1; i2 = i1; v1 = l[e]; i1 = e; }
+      else if (l[e] > v2) { v2 = l[e]; i2 = e; }
     }
-    const int64_t row = row0 + lane;
-    if (lane < kRowsPerWarp && row < num_tokens) {
-      // Ascending scan with strict '>' => the lower index wins a tie
-      // (src/topk_softmax_kernels.cu:39,47 of the reference).
-      float v1 = l[0], v2 = -INFINITY;
-      int i1 = 0, i2 = -1;
+    if (i2 < 0) i2 = (i1 == 0) ? 1 : 0;
+    const float e2 = __expf(v2 - v1);
+    float p1, p2;
+    if (renormalize) {
+      const float inv = 1.0f / (1.0f + e2);
+      p1 = inv;
+      p2 = e2 * inv;
+    } else {
+      float s = 0.f;
 #pragma unroll
-      for (int e = 1; e < kExperts; ++e) {
-        if (l[e] > v1) { v2 = v1; i2 = i1; v1 = l[e]; i1 = e; }
-        else if (l[e] > v2) { v2 = l[e]; i2 = e; }
-      }
-      if (i2 < 0) i2 = (i1 == 0) ? 1 : 0;
-      const float e2 = __expf(v2 - v1);
-      float p1, p2;
-      if (renormalize) {
-        const float inv = 1.0f / (1.0f + e2);
-        p1 = inv;
-        p2 = e2 * inv;
-      } else {
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < kExperts; ++e) s += __expf(l[e] - v1);
-        const float inv = 1.0f / s;
-        p1 = inv;
-        p2 = e2 * inv;
-      }
-      reinterpret_cast<float2*>(weights)[row] = make_float2(p1, p2);
-      reinterpret_cast<int2*>(indices)[row] = make_int2(i1, i2);
-      if (logits_out) {
-        float4* o = reinterpret_cast<float4*>(logits_out + row * kExperts);
-        o[0] = make_float4(l[0], l[1], l[2], l[3]);
-        o[1] = make_float4(l[4], l[5], l[6], l[7]);
-      }
+      for (int e = 0; e < kExperts; ++e) s += __expf(l[e] - v1);
+      const float inv = 1.0f / s;
+      p1 = inv;
+      p2 = e2 * inv;
+    }
+    reinterpret_cast<float2*>(weights)[row] = make_float2(p1, p2);
+    reinterpret_cast<int2*>(indices)[row] = make_int2(i1, i2);
+    if (logits_out) {
+      float4* o = reinterpret_cast<float4*>(logits_out + row * kExperts);
+      o[0] = make_float4(l[0], l[1], l[2], l[3]);
+      o[1] = make_float4(l[4], l[5], l[6], l[7]);
     }
   }
 }
@@ -144,10 +135,6 @@ extern "C" int b200moe_gate_topk_softmax(const void* hidden_states, const void* 
   if (hidden <= 0 || hidden % kChunk != 0)
     return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld must be a positive multiple of %d", name,
                 (long long)hidden, kChunk);
-  const size_t smem = static_cast<size_t>(kExperts) * hidden * 2;
-  if (smem > 200 * 1024)
-    return fail(B200MOE_ERR_SHAPE, "%s: hidden=%lld: the gate weight (%zu bytes) does not fit in shared memory",
-                name, (long long)hidden, smem);
   if (num_tokens < 0) return fail(B200MOE_ERR_SHAPE, "%s: num_tokens=%lld", name, (long long)num_tokens);
   if (num_tokens == 0) return B200MOE_OK;
   if (!hidden_states || !gate_weight || !topk_weights || !topk_indices)
@@ -155,17 +142,9 @@ extern "C" int b200moe_gate_topk_softmax(const void* hidden_states, const void* 
   if (!aligned_to(hidden_states, 16) || !aligned_to(gate_weight, 16) || !aligned_to(topk_weights, 8) ||
       !aligned_to(topk_indices, 8) || (logits_out && !aligned_to(logits_out, 16)))
     return fail(B200MOE_ERR_ALIGN, "%s: pointer alignment", name);
-  const cudaError_t attr = cudaFuncSetAttribute(gate_topk_softmax_kernel,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                static_cast<int>(smem));
-  if (attr != cudaSuccess)
-    return fail(B200MOE_ERR_CUDA, "%s: cannot reserve %zu bytes of shared memory: %s", name, smem,
-                cudaGetErrorString(attr));
-  const int64_t groups = ceil_div64(num_tokens, kRowsPerWarp);
-  int64_t grid = ceil_div64(groups, kWarps);
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 3;  // 3 CTAs of 64 KiB smem fit per SM
-  if (grid > cap) grid = cap;
-  launch_pdl(gate_topk_softmax_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), smem,
+  const int64_t grid = ceil_div64(num_tokens, kRowsPerCta);
+  if (grid > 0x7fffffffLL) return fail(B200MOE_ERR_SHAPE, "%s: num_tokens too large", name);
+  launch_pdl(gate_topk_softmax_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0,
              static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(hidden_states),
              static_cast<const __nv_bfloat16*>(gate_weight), topk_weights, topk_indices, logits_out,
              num_tokens, static_cast<int>(hidden), renormalize, round_logits_bf16);

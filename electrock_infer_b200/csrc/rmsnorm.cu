@@ -32,7 +32,8 @@ template <> struct Elem<float> {
   __device__ static float down(float v) { return v; }
 };
 
-template <typename T, bool kResidual>
+// kNV = 16-byte vectors per thread (1, 2, 4 or 8): the row is held in kNV * kVec registers.
+template <typename T, bool kResidual, int kNV>
 __global__ void __launch_bounds__(kThreads)
 rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual, const T* __restrict__ weight,
                 int hidden, float eps) {
@@ -45,10 +46,10 @@ rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual, const T* __restrict
   T* xrow = x + static_cast<int64_t>(blockIdx.x) * hidden;
   T* rrow = kResidual ? residual + static_cast<int64_t>(blockIdx.x) * hidden : nullptr;
 
-  float vals[kMaxVec][kVec];
+  float vals[kNV][kVec];
   float sq = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
+  for (int i = 0; i < kNV; ++i) {
     const int v = threadIdx.x + i * kThreads;
     if (v < vecs) {
       const uint4 xv = *reinterpret_cast<const uint4*>(xrow + v * kVec);
@@ -85,7 +86,7 @@ rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual, const T* __restrict
   __syncthreads();
   const float scale = s_scale;
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
+  for (int i = 0; i < kNV; ++i) {
     const int v = threadIdx.x + i * kThreads;
     if (v < vecs) {
       const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight + v * kVec));
@@ -109,14 +110,27 @@ int launch(void* x, void* residual, const void* weight, int64_t rows, int64_t hi
   if (hidden % kVec != 0 || hidden > static_cast<int64_t>(kThreads) * kMaxVec * kVec)
     return fail(B200MOE_ERR_SHAPE, "rms_norm: hidden=%lld must be a multiple of %d and at most %d",
                 (long long)hidden, kVec, kThreads * kMaxVec * kVec);
-  if (residual)
-    launch_pdl(rms_norm_kernel<T, true>, dim3(static_cast<unsigned>(rows)), dim3(kThreads), 0, st,
-               static_cast<T*>(x), static_cast<T*>(residual), static_cast<const T*>(weight),
-               static_cast<int>(hidden), eps);
-  else
-    launch_pdl(rms_norm_kernel<T, false>, dim3(static_cast<unsigned>(rows)), dim3(kThreads), 0, st,
-               static_cast<T*>(x), static_cast<T*>(nullptr), static_cast<const T*>(weight),
-               static_cast<int>(hidden), eps);
+  const int vecs = static_cast<int>(hidden / kVec);
+  const int nv = vecs <= kThreads ? 1 : vecs <= 2 * kThreads ? 2 : vecs <= 4 * kThreads ? 4 : 8;
+  const dim3 grid(static_cast<unsigned>(rows)), block(kThreads);
+#define B200MOE_RMS_LAUNCH(RES, NV)                                                              \
+  launch_pdl(rms_norm_kernel<T, RES, NV>, grid, block, 0, st, static_cast<T*>(x),                \
+             static_cast<T*>(residual), static_cast<const T*>(weight), static_cast<int>(hidden), \
+             eps)
+#define B200MOE_RMS_NV(RES)                              \
+  switch (nv) {                                          \
+    case 1: B200MOE_RMS_LAUNCH(RES, 1); break;           \
+    case 2: B200MOE_RMS_LAUNCH(RES, 2); break;           \
+    case 4: B200MOE_RMS_LAUNCH(RES, 4); break;           \
+    default: B200MOE_RMS_LAUNCH(RES, 8); break;          \
+  }
+  if (residual) {
+    B200MOE_RMS_NV(true)
+  } else {
+    B200MOE_RMS_NV(false)
+  }
+#undef B200MOE_RMS_NV
+#undef B200MOE_RMS_LAUNCH
   return check_launch("rms_norm");
 }
 

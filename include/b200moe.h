@@ -85,8 +85,7 @@ int b200moe_topk_softmax(float* topk_weights, int32_t* topk_indices, const void*
  * MixtralMoE.forward (models/mixtral.py:59-61: ReplicatedLinear, layers/linear.py:32-54, followed
  * by fused_topk, layers/moe/fused_moe.py:130-164).
  *
- *   hidden_states bf16 [num_tokens, hidden], gate_weight bf16 [8, hidden]; hidden % 256 == 0 and
- *   8 * hidden * 2 bytes must fit in shared memory (hidden <= 12800)
+ *   hidden_states bf16 [num_tokens, hidden], gate_weight bf16 [8, hidden]; hidden % 256 == 0
  *   logits_out    optional f32 [num_tokens, 8]: the logits the routing decision was made on
  *   round_logits_bf16 != 0 rounds the logits to bf16 first, like the reference's bf16 linear layer
  */

@@ -36,7 +36,8 @@ def _worker(rank, port, mode, result_dir):
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
-    wl = MoEWorkload("par", 600, 512, 1024, seed=23, logit_bias=(2, 1, 0.5, 0, 0, -0.5, -1, -2))
+    tokens = 6 if mode == "ep_peer_tiny" else 600
+    wl = MoEWorkload("par", tokens, 512, 1024, seed=23, logit_bias=(2, 1, 0.5, 0, 0, -0.5, -1, -2))
     full = make_inputs(wl)
     want = moe_oracle.moe_block_ref(full["x"], full["w13"], full["w2"], full["logits"])
     single = fused_experts(full["x"].to(dev), full["w13"].to(dev), full["w2"].to(dev),
@@ -57,13 +58,13 @@ def _worker(rank, port, mode, result_dir):
         res["vs_single"] = moe_oracle.error_stats(out.cpu().float(), single.cpu().float())
     else:
         layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
-                                  exchange="peer" if mode == "ep_peer" else "nccl").to(dev)
+                                  exchange="peer" if mode.startswith("ep_peer") else "nccl").to(dev)
         for e in range(8):
             layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
             layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
             layer.weight_loader(layer.w2_weight, full["w2"][e].to(dev), "w2", e)
-        if mode == "ep_peer":
-            lo, hi = (0, 300) if rank == 0 else (300, 600)  # the peer-memory exchange needs equal splits
+        if mode.startswith("ep_peer"):  # the peer-memory exchange needs equal splits
+            lo, hi = (0, tokens // 2) if rank == 0 else (tokens // 2, tokens)
         else:
             lo, hi = (0, 350) if rank == 0 else (350, 600)  # uneven token split
         x = full["x"][lo:hi].to(dev).clone()
@@ -82,7 +83,7 @@ def _worker(rank, port, mode, result_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["tp", "ep", "ep_peer"])
+@pytest.mark.parametrize("mode", ["tp", "ep", "ep_peer", "ep_peer_tiny"])
 def test_two_gpu_layer(tmp_path, mode):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
