@@ -301,6 +301,20 @@ def test_fused_moe_module_forward():
     assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, st
 
 
+@pytest.mark.parametrize("tp,T", [(2, 1024), (4, 300), (8, 4096), (8, 64)])
+def test_layer_tensor_parallel_shard_shapes(tp, T):
+    """One rank's share of the tensor-parallel layer (intermediate size 14336 / tp, hidden 4096) on
+    a single GPU: the partial output must match the oracle's block evaluated on the same shard."""
+    inter = 14336 // tp
+    wl = MoEWorkload("shard", T, 4096, inter, seed=50 + tp)
+    inp = make_inputs(wl)
+    x, out = run_layer(inp, wl)
+    sample = torch.randperm(T, generator=torch.Generator().manual_seed(1))[:64]
+    want = moe_oracle.moe_block_ref(inp["x"][sample], inp["w13"], inp["w2"], inp["logits"][sample])
+    st = moe_oracle.error_stats(out.cpu().float()[sample], want)
+    assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, st
+
+
 def test_layer_mixtral_decode_shape():
     """Mixtral-8x7B shape, T=256 (the decode-sized configuration), full comparison."""
     wl = WORKLOADS["mixtral_decode_t256"]
