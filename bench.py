@@ -177,6 +177,8 @@ def main():
     ap.add_argument("--parallel", choices=["tp", "ep"], default="ep")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay each step of the device-resident measurement from a CUDA graph")
     ap.add_argument("--block-m", type=int, default=None, choices=[128, 256],
                     help="force the M tile of the grouped GEMMs (default: chosen by batch size)")
     ap.add_argument("--tokens", type=int, default=None,
@@ -257,9 +259,11 @@ def main():
     w13_cpu = w2_cpu = None
     x = torch.empty_like(x0)
 
-    def step():
+    def eager_step():
         x.copy_(x0)  # the layer overwrites its input
         return layer(x, logits)
+
+    step = eager_step
 
     def barrier():
         if world > 1:
@@ -277,6 +281,17 @@ def main():
         for _ in range(args.warmup):
             step()
         barrier()
+        if args.graph and world == 1:
+            cap = torch.cuda.Stream(dev)
+            cap.wait_stream(torch.cuda.current_stream(dev))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=cap):
+                eager_step()
+            torch.cuda.current_stream(dev).wait_stream(cap)
+            step = graph.replay
+            for _ in range(3):
+                step()
+            barrier()
         status = _lib.load().b200moe_gemm_device_status(1)
         if status != 0:
             raise SystemExit(f"grouped GEMM reported device status {status:#x} during warm-up")
@@ -306,7 +321,7 @@ def main():
         fm.enable_kernel_timing(True)
         barrier()
         for _ in range(args.steps):
-            step()
+            eager_step()
         barrier()
         kernel_ms = fm.collect_kernel_timings()
         fm.enable_kernel_timing(False)
@@ -445,6 +460,7 @@ def main():
         "clocks": clocks,
         "kernel_ms": kernels,
         "block_m": fm.choose_block_m(tokens_local, wl.top_k, E),
+        "cuda_graph": bool(args.graph and world == 1),
         "layer_tflops": wl.flops / max(world, 1) / (ms_per_step * 1e-3) / 1e12 if layer_cls is None
         else wl.flops / world / (ms_per_step * 1e-3) / 1e12,
         **extra,

@@ -315,6 +315,36 @@ def test_layer_tensor_parallel_shard_shapes(tp, T):
     assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, st
 
 
+def test_layer_replays_from_a_cuda_graph():
+    """A warmed-up layer call allocates nothing and never synchronises, so it can be captured into
+    a CUDA graph and replayed on new inputs written into the captured buffers."""
+    wl = MoEWorkload("graph", 256, 512, 1024, seed=61)
+    inp = make_inputs(wl)
+    w13, w2 = inp["w13"].to(DEV), inp["w2"].to(DEV)
+    x = inp["x"].to(DEV).clone()
+    logits = inp["logits"].to(DEV).clone()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):  # warm-up on the capture stream: workspace allocation, attribute set-up
+            fused_experts(x, w13, w2, logits, 2, inplace=True)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    x.copy_(inp["x"])
+    with torch.cuda.graph(graph, stream=stream):
+        fused_experts(x, w13, w2, logits, 2, inplace=True)
+    for seed in (62, 63):
+        other = make_inputs(MoEWorkload("graph", 256, 512, 1024, seed=seed))
+        x.copy_(other["x"])
+        logits.copy_(other["logits"])
+        graph.replay()
+        torch.cuda.synchronize()
+        assert gemm_status() == 0
+        want = moe_oracle.moe_block_ref(other["x"], inp["w13"], inp["w2"], other["logits"])
+        st = moe_oracle.error_stats(x.cpu().float(), want)
+        assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, st
+
+
 def test_layer_mixtral_decode_shape():
     """Mixtral-8x7B shape, T=256 (the decode-sized configuration), full comparison."""
     wl = WORKLOADS["mixtral_decode_t256"]
