@@ -52,19 +52,20 @@ def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: i
 
 
 class _Workspace:
-    """Scratch tensors of one ``fused_experts`` call, kept per (device, shape) so that steady-state
-    calls allocate nothing.  The reference allocates its three caches on every call
-    (fused_moe.py:223-239)."""
+    """Scratch tensors of one ``fused_experts`` call, kept per (device, stream, shape) so that
+    steady-state calls allocate nothing and calls on different streams never share scratch.  The
+    reference allocates its three caches on every call (fused_moe.py:223-239)."""
 
     def __init__(self) -> None:
         self._cache: Dict[tuple, dict] = {}
 
     def get(self, device: torch.device, num_tokens: int, topk: int, num_experts: int,
             hidden: int, inter: int, block_m: int) -> dict:
-        key = (device, num_tokens, topk, num_experts, hidden, inter, block_m)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        key = (device, stream, num_tokens, topk, num_experts, hidden, inter, block_m)
         ws = self._cache.get(key)
         if ws is None:
-            if len(self._cache) >= 4:  # bounded: drop the oldest shape
+            if len(self._cache) >= 8:  # bounded: drop the oldest entry
                 self._cache.pop(next(iter(self._cache)))
             pairs = num_tokens * topk
             capacity = pairs + num_experts * (block_m - 1)
