@@ -284,6 +284,8 @@ def main():
         if args.graph and world == 1:
             cap = torch.cuda.Stream(dev)
             cap.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(cap):
+                eager_step()  # the layer's scratch is kept per stream: create it before capturing
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=cap):
                 eager_step()
