@@ -52,7 +52,11 @@ constexpr int kMaxExperts = 64;
 constexpr long long kWaitCycles = 1ll << 31;
 
 constexpr int kSmemAlignSlack = 1024;
-constexpr int kSmemBytes = kStages * kStageBytes + kSmemAlignSlack;
+// Per epilogue warp: 32 rows x 128 bytes of output staged in shared memory (rows padded to 144
+// bytes against bank conflicts) so that global stores cover whole 128-byte lines of a row.
+constexpr int kOutStageRowBytes = 128 + 16;
+constexpr int kOutStageBytes = kEpilogueWarps * 32 * kOutStageRowBytes;  // 18432
+constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kSmemAlignSlack;
 
 // kW13Gather is kW13 with the A rows fetched straight from the token tensor by TMA row gathers.
 enum Mode { kW13 = 0, kW2 = 1, kW13Gather = 2 };
@@ -441,26 +445,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * kBlockN);
       if (kIsW13) {
-        __nv_bfloat16* dst = p.out + slot * p.out_ld + static_cast<long long>(c.n_tile) * p.half_n;
-        const int chunks = p.half_n / 16;
+        // Up to 64 output columns at a time through the warp's staging area, written back eight
+        // lanes per row (see the kW2 branch); the rows of a tile are consecutive rows of act.
+        uint8_t* stage_out = smem + kStages * kStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
+        __nv_bfloat16* tile_dst = p.out +
+            (static_cast<long long>(c.m_block) * kBlockM + quarter * 32) * p.out_ld +
+            static_cast<long long>(c.n_tile) * p.half_n;
 #pragma unroll 1
-        for (int ch = 0; ch < chunks; ++ch) {
-          uint32_t g[16], u[16];
-          tmem_ld_32x16(taddr + ch * 16, g);
-          tmem_ld_32x16(taddr + p.half_n + ch * 16, u);
-          tmem_ld_wait();
-          uint32_t o[8];
+        for (int c0 = 0; c0 < p.half_n; c0 += 64) {
+          const int width = min(64, p.half_n - c0);  // a multiple of 16
+#pragma unroll 1
+          for (int j = 0; j < width; j += 16) {
+            uint32_t g[16], u[16];
+            tmem_ld_32x16(taddr + c0 + j, g);
+            tmem_ld_32x16(taddr + p.half_n + c0 + j, u);
+            tmem_ld_wait();
+            uint32_t o[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-            const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
-            const float a0 = g0 / (1.0f + __expf(-g0)) * u0;
-            const float a1 = g1 / (1.0f + __expf(-g1)) * u1;
-            o[j] = pack_bf16(a0, a1);
+            for (int i = 0; i < 8; ++i) {
+              const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+              const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+              const float a0 = g0 / (1.0f + __expf(-g0)) * u0;
+              const float a1 = g1 / (1.0f + __expf(-g1)) * u1;
+              o[i] = pack_bf16(a0, a1);
+            }
+            uint4* s4 = reinterpret_cast<uint4*>(stage_out + lane * kOutStageRowBytes + j * 2);
+            s4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            s4[1] = make_uint4(o[4], o[5], o[6], o[7]);
           }
-          uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 16);
-          d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          __syncwarp();
+          const int piece = lane & 7;
+          if (piece * 8 < width) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3);
+              const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
+              *reinterpret_cast<uint4*>(tile_dst + static_cast<long long>(r) * p.out_ld + c0 + piece * 8) = o;
+            }
+          }
+          __syncwarp();
         }
       } else {
         const int pair = p.sorted[slot];
@@ -476,13 +499,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           out_row -= owner * p.pairs_per_rank;
         }
         __nv_bfloat16* dst = base + out_row * p.out_ld + static_cast<long long>(c.n_tile) * kBlockN;
+        // 64 columns at a time: every lane scales and packs its own row into the warp's staging
+        // area, then the warp writes the 32 rows back out eight lanes per row, so that each store
+        // instruction covers four whole 128-byte lines (what a peer mapping or L2 likes) instead
+        // of 32 scattered 16-byte pieces.
+        uint8_t* stage_out = smem + kStages * kStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
+        const unsigned long long dst_bits = live ? reinterpret_cast<unsigned long long>(dst) : 0ull;
 #pragma unroll 1
-        for (int ch = 0; ch < kBlockN / 32; ++ch) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + ch * 32, v);
-          tmem_ld_wait();
-          if (live) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 32);
+        for (int ch = 0; ch < kBlockN / 64; ++ch) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + ch * 64 + h * 32, v);
+            tmem_ld_wait();
+            uint4* s4 = reinterpret_cast<uint4*>(stage_out + lane * kOutStageRowBytes + h * 64);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint4 o;
@@ -490,9 +520,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               o.y = pack_bf16(__uint_as_float(v[8 * q + 2]) * w, __uint_as_float(v[8 * q + 3]) * w);
               o.z = pack_bf16(__uint_as_float(v[8 * q + 4]) * w, __uint_as_float(v[8 * q + 5]) * w);
               o.w = pack_bf16(__uint_as_float(v[8 * q + 6]) * w, __uint_as_float(v[8 * q + 7]) * w);
-              d4[q] = o;
+              s4[q] = o;
             }
           }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), piece = lane & 7;
+            const unsigned long long row_dst = __shfl_sync(0xffffffffu, dst_bits, r);
+            if (row_dst != 0ull) {
+              const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
+              *reinterpret_cast<uint4*>(row_dst + static_cast<unsigned long long>(ch) * 128 + piece * 16) = o;
+            }
+          }
+          __syncwarp();
         }
       }
       // Hand the accumulator back to the MMA warp.
