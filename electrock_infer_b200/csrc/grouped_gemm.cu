@@ -18,7 +18,7 @@
 // CTA layout (192 threads, one CTA per SM, grid = number of SMs):
 //   warp 0      TMA producer (one lane)         smem ring of kStages x (A 16 KiB + B 32 KiB)
 //   warp 1      tcgen05.mma issuer (one lane)   owns the TMEM allocation (512 columns = 2 tiles)
-//   warps 2..5  epilogue: tcgen05.ld -> math -> 16-byte global stores
+//   warps 2..5  epilogue: tcgen05.ld -> math -> per-warp smem staging -> 128-byte row stores
 // Two TMEM accumulators let the epilogue of tile i overlap the MMAs of tile i+1.
 //
 // Every mbarrier wait is bounded (about a second of SM clocks).  A wait that runs out sets the
