@@ -1,12 +1,13 @@
 """MoE-layer throughput benchmark: tokens/s of ``FusedMoE.forward`` at Mixtral-8x7B shape.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--parallel tp|ep]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--parallel tp|tp_nccl|ep]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...      # the reference's torch CPU path on the host cores
 
 One step is one pass of the layer over one batch of seeded synthetic tokens.  At one GPU the
 workload is the prefill-sized, skew-routed Mixtral layer (T=8192); at N > 1 it is the T=16384 step
-sharded expert-parallel (default) or tensor-parallel as the reference does (--parallel tp).  Rank 0 prints ONE JSON line:
+sharded expert-parallel (default) or tensor-parallel as the reference does (--parallel tp; tp_nccl
+keeps the reference's NCCL all-reduce).  Rank 0 prints ONE JSON line:
 
   value         tokens/s with inputs resident in HBM (CUDA events around K steps, max over ranks)
   e2e           the same through host buffers: pinned H2D of activations and logits and D2H of the
@@ -174,7 +175,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--parallel", choices=["tp", "ep"], default="ep")
+    ap.add_argument("--parallel", choices=["tp", "tp_nccl", "ep"], default="ep",
+                    help="N > 1: expert parallel, tensor parallel with the all-reduce inside the "
+                         "layer's kernels (tp), or tensor parallel with NCCL's all-reduce (tp_nccl)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--graph", action="store_true",
@@ -240,7 +243,8 @@ def main():
         inp = make_inputs(wl, device=dev, device_rng=True,
                           inter_slice=slice(rank * shard, (rank + 1) * shard) if world > 1 else None)
         layer = FusedMoE(E, wl.top_k, H, I, tp_size=world, params_dtype=torch.bfloat16,
-                         reduce_results=True).to(dev)
+                         reduce_results=True,
+                         tp_exchange="nccl" if args.parallel == "tp_nccl" else "auto").to(dev)
         layer.w13_weight.data.copy_(inp["w13"])
         layer.w2_weight.data.copy_(inp["w2"])
         x0, logits = inp["x"], inp["logits"]

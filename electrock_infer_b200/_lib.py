@@ -56,6 +56,8 @@ SIGNATURES = {
     "b200moe_grouped_gemm_w2_scale_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64,
                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                                    c_int, c_int64, c_int64, c_int, c_void_p]),
+    "b200moe_moe_sum_ranks_push": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int64,
+                                           c_int64, c_int, c_void_p]),
     "b200moe_peer_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
     "b200moe_peer_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "b200moe_peer_close": (c_int, [c_void_p]),

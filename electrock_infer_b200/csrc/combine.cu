@@ -137,6 +137,64 @@ moe_sum_interleaved_scalar_kernel(const T* __restrict__ in, T* __restrict__ out,
     out[i] = Sum<T>::add(in[2 * i], in[2 * i + 1]);
 }
 
+// Combine of the tensor-parallel layer over peer memory.  `in` is this rank's receive buffer
+// [ranks, tokens, 2, hidden]: slot r holds the scaled expert rows that rank r's second GEMM stored
+// here for this rank's slice of the tokens (partial sums over rank r's part of the intermediate
+// dimension).  A token's 2 * ranks rows are added in fp32 in slot order, rounded once, and the
+// result row is stored to row `row_offset + t` of EVERY rank's output tensor through `out_table`:
+// the reduce step and the all-gather step of the all-reduce in one pass.  One rank computes a
+// given row, so every rank ends up with the same bits.
+constexpr int kMaxPushRanks = 8;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+moe_sum_ranks_push_kernel(const T* __restrict__ in, T* const* __restrict__ out_table, int num_ranks,
+                          int64_t row_offset, int64_t tokens, int64_t hidden) {
+  constexpr int kVec = Sum<T>::kVec;
+  __shared__ T* s_out[kMaxPushRanks];
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x < num_ranks) s_out[threadIdx.x] = out_table[threadIdx.x];
+  __syncthreads();
+  const int64_t vec_per_row = hidden / kVec;
+  const int64_t total = tokens * vec_per_row;
+  const int64_t slot = tokens * 2 * hidden;  // elements per rank slot
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t t = i / vec_per_row, c = i - t * vec_per_row;
+    const T* p = in + (t * 2) * hidden + c * kVec;
+    float acc[kVec];
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) acc[j] = 0.f;
+#pragma unroll 4
+    for (int r = 0; r < num_ranks; ++r) {
+      const uint4 a = ld_stream_16(p + r * slot);
+      const uint4 b = ld_stream_16(p + r * slot + hidden);
+      const T* pa = reinterpret_cast<const T*>(&a);
+      const T* pb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) acc[j] = (acc[j] + to_f32(pa[j])) + to_f32(pb[j]);
+    }
+    uint4 o;
+    T* po = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) po[j] = from_f32<T>(acc[j]);
+    const int64_t dst = (row_offset + t) * hidden + c * kVec;
+    for (int r = 0; r < num_ranks; ++r) *reinterpret_cast<uint4*>(s_out[r] + dst) = o;
+  }
+}
+
 inline unsigned grid_for(int64_t work_per_thread_items, int per_thread) {
   int64_t grid = ceil_div64(work_per_thread_items, static_cast<int64_t>(kThreads) * per_thread);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
@@ -173,6 +231,21 @@ int launch(const void* in_v, void* out_v, int64_t tokens, int64_t hidden, int la
   return check_launch("moe_sum");
 }
 
+template <typename T>
+int launch_ranks_push(const void* in_v, void* const* out_table, int num_ranks,
+                             int64_t row_offset, int64_t tokens, int64_t hidden, cudaStream_t st) {
+  constexpr int kVec = Sum<T>::kVec;
+  if (hidden % kVec != 0 || !aligned_to(in_v, 16))
+    return fail(B200MOE_ERR_ALIGN, "moe_sum_ranks_push: hidden must be a multiple of %d and the "
+                "buffers 16-byte aligned", kVec);
+  const int64_t total = tokens * (hidden / kVec);
+  launch_pdl(moe_sum_ranks_push_kernel<T>, dim3(grid_for(total, 1)), dim3(kThreads), 0, st,
+             static_cast<const T*>(in_v), reinterpret_cast<T* const*>(out_table), num_ranks,
+             row_offset, tokens, hidden);
+  return check_launch("moe_sum_ranks_push");
+}
+
+
 }  // namespace
 }  // namespace b200moe
 
@@ -191,5 +264,31 @@ extern "C" int b200moe_moe_sum(const void* input, void* output, int dtype, int64
     case B200MOE_F16: return launch<__half>(input, output, num_tokens, hidden, layout, st);
     case B200MOE_BF16: return launch<__nv_bfloat16>(input, output, num_tokens, hidden, layout, st);
     default: return fail(B200MOE_ERR_DTYPE, "moe_sum: unsupported dtype %d", dtype);
+  }
+}
+
+extern "C" int b200moe_moe_sum_ranks_push(const void* input, void* const* out_table, int num_ranks,
+                                          int64_t row_offset, int dtype, int64_t num_tokens,
+                                          int64_t hidden, int topk, b200moe_stream_t stream) {
+  using namespace b200moe;
+  const char* name = "moe_sum_ranks_push";
+  if (topk != 2) return fail(B200MOE_ERR_SHAPE, "%s: this function is for top_k=2, got %d", name, topk);
+  if (num_ranks < 1 || num_ranks > kMaxPushRanks)
+    return fail(B200MOE_ERR_SHAPE, "%s: num_ranks=%d outside [1, %d]", name, num_ranks, kMaxPushRanks);
+  if (num_tokens < 0 || hidden < 0 || row_offset < 0)
+    return fail(B200MOE_ERR_SHAPE, "%s: num_tokens=%lld hidden=%lld row_offset=%lld", name,
+                (long long)num_tokens, (long long)hidden, (long long)row_offset);
+  if (num_tokens == 0 || hidden == 0) return B200MOE_OK;
+  if (!input || !out_table) return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case B200MOE_F32:
+      return launch_ranks_push<float>(input, out_table, num_ranks, row_offset, num_tokens, hidden, st);
+    case B200MOE_F16:
+      return launch_ranks_push<__half>(input, out_table, num_ranks, row_offset, num_tokens, hidden, st);
+    case B200MOE_BF16:
+      return launch_ranks_push<__nv_bfloat16>(input, out_table, num_ranks, row_offset, num_tokens,
+                                              hidden, st);
+    default: return fail(B200MOE_ERR_DTYPE, "%s: unsupported dtype %d", name, dtype);
   }
 }

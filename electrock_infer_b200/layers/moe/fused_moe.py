@@ -133,7 +133,7 @@ class _timed:
 def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
                   gating_output: Optional[torch.Tensor], topk: int, renormalize: bool = True,
                   inplace: bool = False, activation: str = "silu",
-                  gate_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  gate_weight: Optional[torch.Tensor] = None, tp_reduce=None) -> torch.Tensor:
     """Mixture-of-experts forward for ``hidden_states [T, H]`` (reference fused_moe.py:170-293).
 
     ``w1`` is the stacked gate/up weight ``[E, 2*I, H]`` (gate rows first), ``w2`` is
@@ -142,7 +142,10 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
     Tensors must be bf16 on a CUDA device: there is no other implementation behind this call.
 
     Extension: with ``gate_weight`` (bf16 ``[E, H]``) the gate projection is computed by the router
-    kernel itself and ``gating_output`` may be ``None``.
+    kernel itself and ``gating_output`` may be ``None``.  With ``tp_reduce`` (a
+    ``parallel.TensorParallelReduce`` whose ``usable(num_tokens)`` holds on every rank) the result
+    is also summed over the tensor-parallel ranks: the second GEMM stores its rows into the owning
+    ranks' buffers over NVLink and the combine kernel finishes the all-reduce.
     """
     if activation != "silu":
         raise NotImplementedError(f"Activation {activation} not supported.")
@@ -174,6 +177,12 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
     lib = _lib.load()
     block_m = choose_block_m(num_tokens, topk, num_experts)
     ws = _workspace.get(dev, num_tokens, topk, num_experts, hidden, inter, block_m)
+    peer = None
+    if tp_reduce is not None:
+        if topk != 2 or not tp_reduce.usable(num_tokens):
+            raise RuntimeError("fused_experts: tp_reduce needs top_k=2 and a token count divisible "
+                               "by the tensor-parallel size")
+        peer = tp_reduce.state(num_tokens, topk, hidden, dev)  # set-up on first use
     capacity = ws["capacity"]
     gating = None
     if gate_weight is None:
@@ -206,14 +215,25 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
                 ws["a_sorted"].data_ptr(), w1.data_ptr(), ws["act"].data_ptr(),
                 ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity, num_experts,
                 hidden, inter, block_m, stream), "grouped_gemm_w13_swiglu")
-        with _timed("grouped_gemm_w2_scale"):
-            _lib.check(lib.b200moe_grouped_gemm_w2_scale(
-                ws["act"].data_ptr(), w2.data_ptr(), ws["cache3"].data_ptr(),
-                ws["topk_weights"].data_ptr(), ws["sorted_ids"].data_ptr(),
-                ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
-                num_tokens * topk, num_experts, hidden, inter, block_m, stream),
-                "grouped_gemm_w2_scale")
-        _lib.count_launches(3)
-        with _timed("moe_sum"):
-            _C.moe_sum(ws["cache3"], output)
+        if tp_reduce is None:
+            with _timed("grouped_gemm_w2_scale"):
+                _lib.check(lib.b200moe_grouped_gemm_w2_scale(
+                    ws["act"].data_ptr(), w2.data_ptr(), ws["cache3"].data_ptr(),
+                    ws["topk_weights"].data_ptr(), ws["sorted_ids"].data_ptr(),
+                    ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
+                    num_tokens * topk, num_experts, hidden, inter, block_m, stream),
+                    "grouped_gemm_w2_scale")
+            _lib.count_launches(3)
+            with _timed("moe_sum"):
+                _C.moe_sum(ws["cache3"], output)
+        else:
+            with _timed("grouped_gemm_w2_scale"):
+                _lib.check(lib.b200moe_grouped_gemm_w2_scale_peer(
+                    ws["act"].data_ptr(), w2.data_ptr(), peer["push_table"].data_ptr(),
+                    tp_reduce.world, peer["tokens_per_rank"] * topk,
+                    ws["topk_weights"].data_ptr(), ws["sorted_ids"].data_ptr(),
+                    ws["expert_ids"].data_ptr(), ws["num_post_pad"].data_ptr(), capacity,
+                    num_experts, hidden, inter, block_m, stream), "grouped_gemm_w2_scale_peer")
+            _lib.count_launches(3)
+            tp_reduce.finish(peer, output, topk)
     return output

@@ -22,12 +22,25 @@ class FusedMoE(nn.Module):
     ``forward(hidden_states [T, H], router_logits [T, E])`` overwrites ``hidden_states`` with the
     layer output and returns it (same storage); with ``reduce_results`` and ``tp_size > 1`` the
     result is summed over the default process group first (:114-116).
+
+    Extension: ``tp_exchange`` chooses how that sum is done.  ``"nccl"`` is the reference's
+    all-reduce of the ``[T, H]`` result.  ``"peer"`` does it inside the layer's own kernels over
+    NVLink peer mappings (``parallel.TensorParallelReduce``; needs ``T`` divisible by ``tp_size``
+    and all ranks on one node).  ``"auto"`` (default) uses the peer path when it applies and the
+    result is at least ``PEER_REDUCE_MIN_BYTES`` large, else NCCL.
     """
+
+    PEER_REDUCE_MIN_BYTES = 4 << 20
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
                  tp_size: Optional[int] = None, params_dtype: Optional[torch.dtype] = None,
-                 renormalize: bool = True, reduce_results: bool = False):
+                 renormalize: bool = True, reduce_results: bool = False,
+                 tp_exchange: str = "auto"):
         super().__init__()
+        if tp_exchange not in ("auto", "peer", "nccl"):
+            raise ValueError("tp_exchange must be 'auto', 'peer' or 'nccl'")
+        self.tp_exchange = tp_exchange
+        self._tp_reduce = None
         initialised = dist.is_available() and dist.is_initialized()
         if tp_size is None:
             tp_size = dist.get_world_size() if initialised else 1
@@ -56,12 +69,34 @@ class FusedMoE(nn.Module):
         self.w13_weight.weight_loader = self.weight_loader
         self.w2_weight.weight_loader = self.weight_loader
 
+    def peer_reduce_for(self, hidden_states: torch.Tensor):
+        """The ``TensorParallelReduce`` to hand to ``fused_experts`` for this batch, or None when
+        the sum (if any) is an NCCL all-reduce.  Every rank sees the same token count, so every
+        rank decides the same way."""
+        if not (self.reduce_results and self.tp_size > 1) or self.tp_exchange == "nccl":
+            return None
+        num_tokens, hidden = hidden_states.shape
+        applies = (hidden_states.is_cuda and self.top_k == 2 and self.tp_size <= 8
+                   and self.tp_size == dist.get_world_size() and dist.get_backend() == "nccl"
+                   and num_tokens > 0 and num_tokens % self.tp_size == 0)
+        if self.tp_exchange == "peer":
+            if not applies:
+                raise RuntimeError("tp_exchange='peer' needs CUDA tensors, NCCL, top_k=2, tp_size <= 8 "
+                                   "and a token count divisible by tp_size")
+        elif not applies or num_tokens * hidden * hidden_states.element_size() < self.PEER_REDUCE_MIN_BYTES:
+            return None
+        if self._tp_reduce is None:
+            from ...parallel import TensorParallelReduce
+            self._tp_reduce = TensorParallelReduce()
+        return self._tp_reduce
+
     def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        tp_reduce = self.peer_reduce_for(hidden_states)
         final_hidden_states = fused_experts(
             hidden_states=hidden_states, w1=self.w13_weight, w2=self.w2_weight,
             gating_output=router_logits, topk=self.top_k, renormalize=self.renormalize,
-            inplace=True, activation="silu")
-        if self.reduce_results and self.tp_size > 1:
+            inplace=True, activation="silu", tp_reduce=tp_reduce)
+        if self.reduce_results and self.tp_size > 1 and tp_reduce is None:
             dist.all_reduce(final_hidden_states)
         return final_hidden_states
 
@@ -100,7 +135,7 @@ class MixtralMoE(nn.Module):
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
                  params_dtype: Optional[torch.dtype] = None, tp_size: Optional[int] = None,
-                 prefix: str = "", fuse_gate: bool = True):
+                 prefix: str = "", fuse_gate: bool = True, tp_exchange: str = "auto"):
         super().__init__()
         self.hidden_size = hidden_size
         self.fuse_gate = fuse_gate
@@ -110,7 +145,8 @@ class MixtralMoE(nn.Module):
         self.gate.weight.weight_loader = self._gate_weight_loader
         self.experts = FusedMoE(num_experts=num_experts, top_k=top_k, hidden_size=hidden_size,
                                 intermediate_size=intermediate_size, params_dtype=params_dtype,
-                                reduce_results=True, renormalize=True, tp_size=tp_size)
+                                reduce_results=True, renormalize=True, tp_size=tp_size,
+                                tp_exchange=tp_exchange)
 
     @staticmethod
     def _gate_weight_loader(param: nn.Parameter, loaded_weight: torch.Tensor) -> None:
@@ -121,10 +157,11 @@ class MixtralMoE(nn.Module):
         orig_shape = hidden_states.shape
         hidden_states = hidden_states.view(-1, self.hidden_size)
         if self.fuse_gate:
+            tp_reduce = self.experts.peer_reduce_for(hidden_states)
             out = fused_experts(hidden_states, self.experts.w13_weight, self.experts.w2_weight, None,
                                 self.experts.top_k, renormalize=True, inplace=True,
-                                gate_weight=self.gate.weight)
-            if self.experts.tp_size > 1:
+                                gate_weight=self.gate.weight, tp_reduce=tp_reduce)
+            if self.experts.tp_size > 1 and tp_reduce is None:
                 dist.all_reduce(out)
         else:
             out = self.experts(hidden_states, self.gate(hidden_states))

@@ -92,6 +92,69 @@ class PeerBuffer:
         self.ptrs = []
 
 
+class TensorParallelReduce:
+    """The all-reduce of the tensor-parallel layer done by the layer's own kernels over NVLink
+    peer mappings instead of an NCCL all-reduce of the ``[T, H]`` result.
+
+    Rank ``j`` owns the token slice ``[j * T / tp, (j + 1) * T / tp)``:
+
+        second grouped GEMM: the epilogue STORES the scaled rows of slice ``j`` into rank ``j``'s
+        receive buffer, slot = source rank (``b200moe_grouped_gemm_w2_scale_peer``)
+        -> one-word all-reduce (every rank's GEMM has finished)
+        -> ``b200moe_moe_sum_ranks_push``: adds the ``tp * top_k`` rows of each own token in fp32,
+           rounds once and stores the row into EVERY rank's output buffer
+        -> one-word all-reduce (every rank's rows have landed) -> copy into ``hidden_states``
+
+    No kernel waits on a flag: the ranks are ordered by the two tiny stream-ordered collectives.
+    The sum differs from the reference's in rounding only (the reference rounds each rank's
+    two-row sum to bf16 and then all-reduces in bf16, layers/moe/mixtral_moe.py:114-116); every
+    rank receives the same bits.  ``state`` allocates and synchronises the first time a token
+    count is seen.
+    """
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._states = {}
+
+    def usable(self, num_tokens: int) -> bool:
+        return num_tokens > 0 and num_tokens % self.world == 0 and self.world <= 8
+
+    def state(self, num_tokens: int, top_k: int, hidden: int, device: torch.device) -> dict:
+        key = (num_tokens, top_k, hidden, device)
+        st = self._states.get(key)
+        if st is None:
+            per = num_tokens // self.world
+            slot_bytes = per * top_k * hidden * 2
+            recv = PeerBuffer(self.world * slot_bytes, device, self.group)
+            out = PeerBuffer(num_tokens * hidden * 2, device, self.group)
+            st = {
+                "recv": recv, "out": out, "tokens_per_rank": per,
+                # Where this rank's rows go in every rank's receive buffer.
+                "push_table": torch.tensor([p + self.rank * slot_bytes for p in recv.ptrs],
+                                           dtype=torch.int64, device=device),
+                "out_local": out.local.view(torch.bfloat16).view(num_tokens, hidden),
+                "token": torch.zeros(1, dtype=torch.int32, device=device),
+            }
+            self._states[key] = st
+        return st
+
+    def finish(self, st: dict, output: torch.Tensor, top_k: int) -> None:
+        """Everything after the second GEMM: barrier, combine + push, barrier, copy."""
+        num_tokens, hidden = output.shape
+        dist.all_reduce(st["token"], group=self.group)
+        with _timed("moe_sum_ranks_push"):
+            _lib.check(_lib.load().b200moe_moe_sum_ranks_push(
+                st["recv"].local.data_ptr(), st["out"].table.data_ptr(), self.world,
+                self.rank * st["tokens_per_rank"], _lib.BF16,
+                st["tokens_per_rank"], hidden, top_k,
+                torch.cuda.current_stream(output.device).cuda_stream), "moe_sum_ranks_push")
+        _lib.count_launches(1)
+        dist.all_reduce(st["token"], group=self.group)
+        output.copy_(st["out_local"])
+
+
 class CudaOps:
     """The arithmetic steps of the expert-parallel layer on the local GPU (C-ABI calls)."""
 

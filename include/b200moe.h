@@ -310,6 +310,26 @@ int b200moe_grouped_gemm_w2_scale_peer(const void* act, const void* w2, void* co
                                        b200moe_stream_t stream);
 
 /*
+ * Tensor-parallel combine over NVLink (no reference counterpart: the reference adds the ranks'
+ * partial layer outputs with an NCCL all-reduce, layers/moe/mixtral_moe.py:114-116).
+ *
+ * With the intermediate dimension sharded over num_ranks GPUs, every rank's second GEMM
+ * (b200moe_grouped_gemm_w2_scale_peer with out_table[j] = rank j's receive buffer + this rank's
+ * slot) stores the rows of token slice j straight into rank j's receive buffer
+ * input [num_ranks, num_tokens, 2, hidden] (num_tokens = tokens per slice).  This function then
+ * adds a token's 2 * num_ranks rows in fp32 in slot order, rounds once to the element type and
+ * stores the result row to row (row_offset + t) of the [*, hidden] tensor at out_table[j] for
+ * EVERY j (a DEVICE array of num_ranks device pointers, local memory or peer mappings):
+ * reduce-scatter and all-gather of the all-reduce without a separate collective.  The caller
+ * orders the ranks around it with stream-ordered collectives (all second GEMMs done before this
+ * call; all calls done before the outputs are read).  num_ranks <= 8, topk must be 2, hidden a
+ * multiple of 16 bytes.
+ */
+int b200moe_moe_sum_ranks_push(const void* input, void* const* out_table, int num_ranks,
+                               int64_t row_offset, int dtype, int64_t num_tokens, int64_t hidden,
+                               int topk, b200moe_stream_t stream);
+
+/*
  * Set-up helpers for peer-visible buffers (these DO allocate and synchronise; not for the hot
  * path).  b200moe_peer_alloc: cudaMalloc + zero fill + CUDA IPC handle (64 bytes) for the other
  * rank processes of the node.  b200moe_peer_open maps another process's buffer from its handle;

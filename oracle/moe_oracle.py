@@ -163,6 +163,19 @@ def moe_sum_efficient_ref(x: torch.Tensor) -> torch.Tensor:
     return x[..., 0] + x[..., 1]
 
 
+def moe_sum_ranks_ref(x: torch.Tensor) -> torch.Tensor:
+    """``[R, T, 2, H] -> [T, H]``: the combine of the tensor-parallel layer when the ranks' partial
+    rows meet in one buffer: fp32 sum over rank-major then expert-slot order, rounded once to the
+    element type.  (The reference instead rounds each rank's two-row sum and all-reduces in the
+    element type, layers/moe/mixtral_moe.py:114-116; the sums differ in rounding only.)"""
+    x = x.detach().cpu()
+    acc = torch.zeros(x.shape[1], x.shape[3], dtype=torch.float32)
+    for r in range(x.shape[0]):
+        for k in range(x.shape[2]):
+            acc = acc + x[r, :, k].to(torch.float32)
+    return acc.to(x.dtype)
+
+
 def rms_norm_ref(x: torch.Tensor, weight: torch.Tensor, eps: float,
                  residual: Optional[torch.Tensor] = None):
     """RMSNorm, optionally after a residual add, as the reference runs it

@@ -176,6 +176,84 @@ def test_peer_table_kernels_on_one_gpu():
     assert (out0 == 5.0).all(dim=1).sum().item() == int((ids < 0).sum() + (ids >= E).sum())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("ranks,T_loc,H", [(2, 33, 256), (3, 7, 64), (8, 40, 512), (1, 5, 128)])
+def test_moe_sum_ranks_push(ranks, T_loc, H, dtype):
+    """fp32 sum over ranks * 2 rows in slot order, one rounding, the row stored to every rank's output."""
+    g = torch.Generator().manual_seed(ranks * 100 + T_loc)
+    recv = torch.randn(ranks, T_loc, 2, H, generator=g).to(dtype)
+    d_recv = recv.to(DEV)
+    row_offset = 3
+    outs = [torch.full((row_offset + T_loc + 2, H), 7.0, dtype=dtype, device=DEV) for _ in range(ranks)]
+    table = torch.tensor([o.data_ptr() for o in outs], dtype=torch.int64, device=DEV)
+    _lib.check(_lib.load().b200moe_moe_sum_ranks_push(
+        d_recv.data_ptr(), table.data_ptr(), ranks, row_offset, _C._FLOAT_TAGS[dtype], T_loc, H, 2,
+        torch.cuda.current_stream().cuda_stream), "moe_sum_ranks_push")
+    torch.cuda.synchronize()
+    want = moe_oracle.moe_sum_ranks_ref(recv)
+    for o in outs:
+        assert torch.equal(o[row_offset:row_offset + T_loc].cpu(), want)
+        assert (o[:row_offset] == 7.0).all() and (o[row_offset + T_loc:] == 7.0).all()
+
+
+def test_tensor_parallel_peer_path_on_one_gpu():
+    """The tensor-parallel layer with its all-reduce inside the kernels, both "ranks" played on one
+    GPU one after the other: each rank's second GEMM stores the rows of token slice j into slot r
+    of receive buffer j, then the combine of slice j adds all slots and stores to every output."""
+    lib = _lib.load()
+    ranks, T, H, I, E, k = 2, 384, 512, 1024, 8, 2
+    T_loc, I_loc = T // ranks, I // ranks
+    wl = MoEWorkload("tp1", T, H, I, seed=41, logit_bias=(1, 0, 0, 0, 0, 0, 0, -1))
+    inp = make_inputs(wl)
+    x = inp["x"].to(DEV)
+    tw, ids = fused_topk(x, inp["logits"].to(DEV), k, True)
+    s, e, n = aligned(ids.cpu().numpy().reshape(-1), E)
+    cap = s.size
+    d_s, d_e, d_n = torch.from_numpy(s).to(DEV), torch.from_numpy(e).to(DEV), torch.from_numpy(n).to(DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    a = torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.b200moe_gather_rows(x.data_ptr(), a.data_ptr(), d_s.data_ptr(), d_n.data_ptr(), cap,
+                                       T, H, k, stream), "gather_rows")
+    slot = T_loc * k * H
+    recv = [torch.full((ranks * slot,), 3.0, dtype=torch.bfloat16, device=DEV) for _ in range(ranks)]
+    local = []
+    keep = []
+    for r in range(ranks):
+        w1 = inp["w13"][:, r * I_loc:(r + 1) * I_loc]
+        w3 = inp["w13"][:, I + r * I_loc:I + (r + 1) * I_loc]
+        w13_r = torch.cat([w1, w3], dim=1).contiguous().to(DEV)
+        w2_r = inp["w2"][:, :, r * I_loc:(r + 1) * I_loc].contiguous().to(DEV)
+        act = torch.empty(cap, I_loc, dtype=torch.bfloat16, device=DEV)
+        _lib.check(lib.b200moe_grouped_gemm_w13_swiglu(a.data_ptr(), w13_r.data_ptr(), act.data_ptr(),
+                                                       d_e.data_ptr(), d_n.data_ptr(), cap, E, H, I_loc,
+                                                       128, stream), "w13")
+        out_r = torch.empty(T * k, H, dtype=torch.bfloat16, device=DEV)
+        _lib.check(lib.b200moe_grouped_gemm_w2_scale(
+            act.data_ptr(), w2_r.data_ptr(), out_r.data_ptr(), tw.data_ptr(), d_s.data_ptr(),
+            d_e.data_ptr(), d_n.data_ptr(), cap, T * k, E, H, I_loc, 128, stream), "w2")
+        push = torch.tensor([b.data_ptr() + r * slot * 2 for b in recv], dtype=torch.int64, device=DEV)
+        _lib.check(lib.b200moe_grouped_gemm_w2_scale_peer(
+            act.data_ptr(), w2_r.data_ptr(), push.data_ptr(), ranks, T_loc * k, tw.data_ptr(),
+            d_s.data_ptr(), d_e.data_ptr(), d_n.data_ptr(), cap, E, H, I_loc, 128, stream), "w2 peer")
+        local.append(out_r)
+        keep += [w13_r, w2_r, act, push]
+    outs = [torch.empty(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(ranks)]
+    table = torch.tensor([o.data_ptr() for o in outs], dtype=torch.int64, device=DEV)
+    for j in range(ranks):
+        _lib.check(lib.b200moe_moe_sum_ranks_push(recv[j].data_ptr(), table.data_ptr(), ranks, j * T_loc,
+                                                  _lib.BF16, T_loc, H, k, stream), "moe_sum_ranks_push")
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    assert torch.equal(outs[0], outs[1])
+    # Bit-exact against the restated combine over the ranks' locally computed rows ...
+    stacked = torch.stack([o.view(T, k, H) for o in local]).cpu()
+    assert torch.equal(outs[0].cpu(), moe_oracle.moe_sum_ranks_ref(stacked))
+    # ... and within the layer tolerance of the fp32 block.
+    want = moe_oracle.moe_block_ref(inp["x"], inp["w13"], inp["w2"], inp["logits"])
+    st = moe_oracle.error_stats(outs[0].cpu().float(), want)
+    assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, st
+
+
 # --------------------------------------------------------------------------------- whole layer
 def run_layer(inp, wl, inplace=True):
     x = inp["x"].to(torch.bfloat16).to(DEV).clone()

@@ -43,9 +43,11 @@ def _worker(rank, port, mode, result_dir):
     single = fused_experts(full["x"].to(dev), full["w13"].to(dev), full["w2"].to(dev),
                            full["logits"].to(dev), 2, inplace=False)
     res = {}
-    if mode == "tp":  # noqa: SIM102
+    if mode.startswith("tp"):
+        # "tp": the reference's NCCL all-reduce; "tp_peer": the all-reduce inside the layer's kernels.
         layer = FusedMoE(8, 2, wl.hidden, wl.inter, tp_size=WORLD, params_dtype=torch.bfloat16,
-                         reduce_results=True).to(dev)
+                         reduce_results=True,
+                         tp_exchange="peer" if mode == "tp_peer" else "nccl").to(dev)
         for e in range(8):
             layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
             layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
@@ -56,6 +58,15 @@ def _worker(rank, port, mode, result_dir):
         res["alias"] = out.data_ptr() == x.data_ptr()
         res["stats"] = moe_oracle.error_stats(out.cpu().float(), want)
         res["vs_single"] = moe_oracle.error_stats(out.cpu().float(), single.cpu().float())
+        if mode == "tp_peer":
+            # Every rank must hold the same bits, and a second call must reuse the buffers cleanly.
+            both = [torch.empty_like(out) for _ in range(WORLD)]
+            dist.all_gather(both, out)
+            res["ranks_agree"] = bool(torch.equal(both[0], both[1]))
+            x2 = full["x"].to(dev).flip(0).contiguous()
+            out2 = layer(x2, full["logits"].to(dev).flip(0).contiguous())
+            torch.cuda.synchronize()
+            res["second_call"] = bool(torch.equal(out2, out.flip(0)))
     else:
         layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
                                   exchange="peer" if mode.startswith("ep_peer") else "nccl").to(dev)
@@ -83,7 +94,7 @@ def _worker(rank, port, mode, result_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["tp", "ep", "ep_peer", "ep_peer_tiny"])
+@pytest.mark.parametrize("mode", ["tp", "tp_peer", "ep", "ep_peer", "ep_peer_tiny"])
 def test_two_gpu_layer(tmp_path, mode):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
@@ -98,3 +109,5 @@ def test_two_gpu_layer(tmp_path, mode):
         else:
             # TP sums two bf16-rounded partial outputs: close to, not identical with, one GPU.
             assert r["vs_single"]["rel_fro"] <= 1e-2, r
+            if mode == "tp_peer":
+                assert r["ranks_agree"] and r["second_call"], r

@@ -107,7 +107,8 @@ def _tp_worker(rank, port, result_dir):
     full = make_inputs(wl)
 
     def cpu_fused_experts(hidden_states, w1, w2, gating_output, topk, renormalize, inplace,
-                          activation):
+                          activation, tp_reduce=None):
+        assert tp_reduce is None  # CPU tensors / gloo: the sum stays a process-group all-reduce
         out = moe_oracle.moe_block_ref(hidden_states, w1, w2, gating_output, topk, renormalize)
         hidden_states.copy_(out)
         return hidden_states
@@ -125,7 +126,16 @@ def _tp_worker(rank, port, result_dir):
     x = full["x"].clone()
     out = layer(x, full["logits"])
     want = moe_oracle.moe_block_ref(full["x"], full["w13"], full["w2"], full["logits"])
-    torch.save({"err": (out - want).abs().max().item(), "alias": out.data_ptr() == x.data_ptr()},
+    # The in-kernel all-reduce is refused, not silently replaced, where it cannot run.
+    forced = FusedMoE(wl.num_experts, 2, wl.hidden, wl.inter, tp_size=WORLD,
+                      params_dtype=torch.float32, reduce_results=True, tp_exchange="peer")
+    try:
+        forced.peer_reduce_for(torch.zeros(34, wl.hidden))
+        refused = False
+    except RuntimeError:
+        refused = True
+    torch.save({"err": (out - want).abs().max().item(), "alias": out.data_ptr() == x.data_ptr(),
+                "refused": refused},
                os.path.join(result_dir, f"tp{rank}.pt"))
     dist.destroy_process_group()
 
@@ -134,7 +144,7 @@ def test_tensor_parallel_all_reduce_on_gloo(tmp_path):
     mp.spawn(_tp_worker, args=(_free_port(), str(tmp_path)), nprocs=WORLD, join=True)
     for rank in range(WORLD):
         r = torch.load(tmp_path / f"tp{rank}.pt")
-        assert r["alias"] and r["err"] < 1e-4, r
+        assert r["alias"] and r["err"] < 1e-4 and r["refused"], r
 
 
 def test_split_sizes_and_row_experts():
