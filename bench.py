@@ -44,6 +44,10 @@ UNIT = "tokens/s"
 # T=2048 case: 2.075 GB against 2.050 GB of algorithmic bytes (weights + A rows + output rows).
 # Traffic is weights + rows x (H + I') x 2 bytes, so a full-size launch is scaled by the same ratio.
 NCU_TRAFFIC_RATIO = 2.075 / 2.050
+# Device buffers of the end-to-end pipeline: step i+3's upload waits for step i's download (the
+# layer writes its result over its input), so three buffers let upload, kernels and download of
+# neighbouring steps all overlap.
+E2E_BUFFERS = 3
 NCU_TRAFFIC_NOTE = ("algorithmic bytes x 1.012, the ncu DRAM read+write / algorithmic ratio of the "
                     "T=2048 capture (profiles/grouped_gemm_t2048_ncu_full.txt)")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -333,8 +337,9 @@ def main():
         fm.enable_kernel_timing(False)
 
         # ---- end to end through host buffers: every step copies its inputs from pinned host
-        # memory and copies its result back; copies and compute run on three streams with two
-        # device buffers, so step i+1's upload and step i-1's download overlap step i's kernels.
+        # memory and copies its result back; copies and compute run on three streams with
+        # E2E_BUFFERS device buffers, so step i+1's upload and step i-1's download overlap step i's
+        # kernels.
         # Tensor parallel needs the same activations on every rank: each rank uploads 1/N of the
         # batch and the ranks all-gather over NVLink, and each rank downloads 1/N of the (replicated)
         # result.  Expert parallel is token-sharded to begin with.
@@ -343,22 +348,23 @@ def main():
         lo = rank * t_loc if tp_split else 0
         xh = x0[lo:lo + t_loc].cpu().pin_memory()
         lh = logits[lo:lo + t_loc].cpu().pin_memory()
-        oh = [torch.empty_like(xh).pin_memory() for _ in range(2)]
-        xd = [torch.empty_like(x0) for _ in range(2)]
-        ld = [torch.empty_like(logits) for _ in range(2)]
-        xs = [torch.empty_like(x0[:t_loc]) for _ in range(2)] if tp_split else xd
-        ls = [torch.empty_like(logits[:t_loc]) for _ in range(2)] if tp_split else ld
+        nbuf = E2E_BUFFERS
+        oh = [torch.empty_like(xh).pin_memory() for _ in range(nbuf)]
+        xd = [torch.empty_like(x0) for _ in range(nbuf)]
+        ld = [torch.empty_like(logits) for _ in range(nbuf)]
+        xs = [torch.empty_like(x0[:t_loc]) for _ in range(nbuf)] if tp_split else xd
+        ls = [torch.empty_like(logits[:t_loc]) for _ in range(nbuf)] if tp_split else ld
         s_in, s_c, s_out = (torch.cuda.Stream(dev) for _ in range(3))
-        ev_in = [torch.cuda.Event() for _ in range(2)]
-        ev_done = [torch.cuda.Event() for _ in range(2)]
-        ev_out = [torch.cuda.Event() for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(nbuf)]
+        ev_done = [torch.cuda.Event() for _ in range(nbuf)]
+        ev_out = [torch.cuda.Event() for _ in range(nbuf)]
 
         def e2e_run(n):
             main = torch.cuda.current_stream(dev)
             for st in (s_in, s_c, s_out):
                 st.wait_stream(main)
             for i in range(n):
-                b = i & 1
+                b = i % nbuf
                 with torch.cuda.stream(s_in):
                     s_in.wait_event(ev_out[b])   # the result that aliases xd[b] has been downloaded
                     xs[b].copy_(xh, non_blocking=True)
@@ -459,7 +465,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": (xh.numel() * 2 + lh.numel() * 4) * world,
                 "d2h_bytes_per_step": oh[0].numel() * 2 * world,
-                "overlap": "3 streams, 2 device buffers: uploads/downloads overlap the kernels"},
+                "overlap": f"3 streams, {E2E_BUFFERS} device buffers: uploads/downloads overlap the kernels"},
         "gpu_launches": launches,
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
