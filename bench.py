@@ -154,8 +154,8 @@ def run_reference(args, wl: MoEWorkload):
         "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": mean * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(wl, args, world),
-        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": sample_desc},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "cpu_model": cpu_model(),
+                         "kind": "port", "sample": sample_desc},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -172,6 +172,17 @@ def workload_config(wl: MoEWorkload, args, world: int) -> dict:
 
 
 # --------------------------------------------------------------------------------------- our arm
+def cpu_model() -> str:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for ln in f:
+                if ln.lower().startswith("model name"):
+                    return ln.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -453,7 +464,8 @@ def main():
         sample = min(T, args.cpu_sample_tokens)
         cores = os.cpu_count() or 1
         tps, mean = cpu_block_tokens_per_s(wl, inp, sample, 5, 1, torch.bfloat16)
-        cpu_baseline = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+        cpu_baseline = {"value": tps, "unit": UNIT, "cores": cores, "cpu_model": cpu_model(),
+                        "kind": "port",
                         "sample": f"first {sample} of {T} tokens of {wl.name}, bf16 torch CPU block, "
                                   f"1 warm-up + 5 timed passes ({mean:.2f} s each)"}
 

@@ -140,10 +140,14 @@ moe_sum_interleaved_scalar_kernel(const T* __restrict__ in, T* __restrict__ out,
 // Combine of the tensor-parallel layer over peer memory.  `in` is this rank's receive buffer
 // [ranks, tokens, 2, hidden]: slot r holds the scaled expert rows that rank r's second GEMM stored
 // here for this rank's slice of the tokens (partial sums over rank r's part of the intermediate
-// dimension).  A token's 2 * ranks rows are added in fp32 in slot order, rounded once, and the
-// result row is stored to row `row_offset + t` of EVERY rank's output tensor through `out_table`:
-// the reduce step and the all-gather step of the all-reduce in one pass.  One rank computes a
-// given row, so every rank ends up with the same bits.
+// dimension).  Each slot's two rows are first added and rounded to the element type exactly as
+// moe_sum does on a rank of its own (the reference's tensor-parallel ranks round their partial
+// result before the all-reduce, layers/moe/fused_moe.py:291 then mixtral_moe.py:114-116);
+// the per-slot sums are then added in fp32 in slot order and rounded once, which for two ranks is
+// the correctly rounded sum an all-reduce of the two partial results gives.  The result row is
+// stored to row `row_offset + t` of EVERY rank's output tensor through `out_table`: the reduce
+// step and the all-gather step of the all-reduce in one pass.  One rank computes a given row, so
+// every rank ends up with the same bits.
 constexpr int kMaxPushRanks = 8;
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
@@ -184,7 +188,7 @@ moe_sum_ranks_push_kernel(const T* __restrict__ in, T* const* __restrict__ out_t
       const T* pa = reinterpret_cast<const T*>(&a);
       const T* pb = reinterpret_cast<const T*>(&b);
 #pragma unroll
-      for (int j = 0; j < kVec; ++j) acc[j] = (acc[j] + to_f32(pa[j])) + to_f32(pb[j]);
+      for (int j = 0; j < kVec; ++j) acc[j] += to_f32(Sum<T>::add0(pa[j], pb[j]));
     }
     uint4 o;
     T* po = reinterpret_cast<T*>(&o);

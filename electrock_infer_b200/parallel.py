@@ -64,6 +64,7 @@ class PeerBuffer:
         lib = _lib.load()
         self._lib = lib
         self.nbytes = nbytes
+        self.group = group
         self.rank = dist.get_rank(group)
         world = dist.get_world_size(group)
         own = ctypes.c_void_p()
@@ -85,11 +86,19 @@ class PeerBuffer:
         self.local = torch.as_tensor(_RawDeviceMemory(own.value, nbytes), device=device)
 
     def close(self) -> None:
+        """Collective over the group: every rank unmaps the other ranks' buffers, and only when
+        all have done so does each rank free its own (an allocation must outlive its mappings in
+        other processes).  Call it with no work on the buffers in flight."""
+        if not self.ptrs:
+            return
+        torch.cuda.synchronize(self.local.device)
         for r, ptr in enumerate(self.ptrs):
             if r != self.rank:
                 self._lib.b200moe_peer_close(ptr)
+        dist.barrier(group=self.group)
         self._lib.b200moe_peer_free(self.ptrs[self.rank])
         self.ptrs = []
+        self.local = None
 
 
 class TensorParallelReduce:
@@ -101,14 +110,16 @@ class TensorParallelReduce:
         second grouped GEMM: the epilogue STORES the scaled rows of slice ``j`` into rank ``j``'s
         receive buffer, slot = source rank (``b200moe_grouped_gemm_w2_scale_peer``)
         -> one-word all-reduce (every rank's GEMM has finished)
-        -> ``b200moe_moe_sum_ranks_push``: adds the ``tp * top_k`` rows of each own token in fp32,
-           rounds once and stores the row into EVERY rank's output buffer
+        -> ``b200moe_moe_sum_ranks_push``: sums each own token's rows (per source rank like
+           ``moe_sum``, then over the ranks in fp32 with one rounding) and stores the row into
+           EVERY rank's output buffer
         -> one-word all-reduce (every rank's rows have landed) -> copy into ``hidden_states``
 
     No kernel waits on a flag: the ranks are ordered by the two tiny stream-ordered collectives.
-    The sum differs from the reference's in rounding only (the reference rounds each rank's
-    two-row sum to bf16 and then all-reduces in bf16, layers/moe/mixtral_moe.py:114-116); every
-    rank receives the same bits.  ``state`` allocates and synchronises the first time a token
+    Rounding follows the reference (each rank's two-row sum is rounded to bf16 before the ranks
+    are added, layers/moe/mixtral_moe.py:114-116): with two ranks the result has the same bits as
+    the NCCL all-reduce; with more it is one fp32 sum in rank order, where an all-reduce rounds
+    between its steps in an order of its own choosing.  Every rank receives the same bits.  ``state`` allocates and synchronises the first time a token
     count is seen.
     """
 
@@ -139,6 +150,14 @@ class TensorParallelReduce:
             }
             self._states[key] = st
         return st
+
+    def close(self) -> None:
+        """Unmaps and frees the peer-visible buffers (every rank, after the last step has
+        finished on every rank)."""
+        for st in self._states.values():
+            st["recv"].close()
+            st["out"].close()
+        self._states.clear()
 
     def finish(self, st: dict, output: torch.Tensor, top_k: int) -> None:
         """Everything after the second GEMM: barrier, combine + push, barrier, copy."""
@@ -361,6 +380,15 @@ class ExpertParallelMoE(nn.Module):
             }
         self._peer_states[key] = state
         return state
+
+    def close(self) -> None:
+        """Unmaps and frees the peer-visible buffers of the peer-memory exchange (every rank,
+        after the last step has finished on every rank)."""
+        for st in self._peer_states.values():
+            if st is not None:
+                st["x_stage"].close()
+                st["cache3"].close()
+        self._peer_states.clear()
 
     def _forward_peer(self, st: dict, hidden_states: torch.Tensor,
                       router_logits: torch.Tensor) -> torch.Tensor:

@@ -317,7 +317,8 @@ int b200moe_grouped_gemm_w2_scale_peer(const void* act, const void* w2, void* co
  * (b200moe_grouped_gemm_w2_scale_peer with out_table[j] = rank j's receive buffer + this rank's
  * slot) stores the rows of token slice j straight into rank j's receive buffer
  * input [num_ranks, num_tokens, 2, hidden] (num_tokens = tokens per slice).  This function then
- * adds a token's 2 * num_ranks rows in fp32 in slot order, rounds once to the element type and
+ * adds each slot's two rows and rounds like b200moe_moe_sum (the per-rank partial result of the
+ * reference), adds the per-slot sums in fp32 in slot order, rounds once to the element type and
  * stores the result row to row (row_offset + t) of the [*, hidden] tensor at out_table[j] for
  * EVERY j (a DEVICE array of num_ranks device pointers, local memory or peer mappings):
  * reduce-scatter and all-gather of the all-reduce without a separate collective.  The caller

@@ -165,14 +165,15 @@ def moe_sum_efficient_ref(x: torch.Tensor) -> torch.Tensor:
 
 def moe_sum_ranks_ref(x: torch.Tensor) -> torch.Tensor:
     """``[R, T, 2, H] -> [T, H]``: the combine of the tensor-parallel layer when the ranks' partial
-    rows meet in one buffer: fp32 sum over rank-major then expert-slot order, rounded once to the
-    element type.  (The reference instead rounds each rank's two-row sum and all-reduces in the
-    element type, layers/moe/mixtral_moe.py:114-116; the sums differ in rounding only.)"""
+    rows meet in one buffer.  Each rank's two rows are summed and rounded to the element type as
+    ``moe_sum`` does on that rank (the reference's ranks round their partial result before the
+    all-reduce, layers/moe/fused_moe.py:291, layers/moe/mixtral_moe.py:114-116); the per-rank
+    sums are then added in fp32 in rank order and rounded once.  For two ranks that is exactly the
+    correctly rounded sum of the two partial results, i.e. what the all-reduce returns."""
     x = x.detach().cpu()
     acc = torch.zeros(x.shape[1], x.shape[3], dtype=torch.float32)
     for r in range(x.shape[0]):
-        for k in range(x.shape[2]):
-            acc = acc + x[r, :, k].to(torch.float32)
+        acc = acc + moe_sum_ref(x[r]).to(torch.float32)
     return acc.to(x.dtype)
 
 

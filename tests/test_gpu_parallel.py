@@ -67,6 +67,12 @@ def _worker(rank, port, mode, result_dir):
             out2 = layer(x2, full["logits"].to(dev).flip(0).contiguous())
             torch.cuda.synchronize()
             res["second_call"] = bool(torch.equal(out2, out.flip(0)))
+            # With two ranks the in-kernel sum rounds where the reference does (each rank's partial
+            # result to bf16, then one correctly rounded add): same bits as the NCCL all-reduce.
+            layer.tp_exchange = "nccl"
+            out3 = layer(full["x"].to(dev).clone(), full["logits"].to(dev))
+            torch.cuda.synchronize()
+            res["equals_nccl"] = bool(torch.equal(out3, out))
     else:
         layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
                                   exchange="peer" if mode.startswith("ep_peer") else "nccl").to(dev)
@@ -90,6 +96,12 @@ def _worker(rank, port, mode, result_dir):
         torch.cuda.synchronize()
         res["bit_exact_second_call"] = bool(torch.equal(out2, single[lo:hi].flip(0)))
     res["gemm_status"] = _lib.load().b200moe_gemm_device_status(1)
+    # Release the peer-visible buffers once every rank has finished with them.
+    dist.barrier()
+    if mode == "tp_peer":
+        layer._tp_reduce.close()
+    elif mode.startswith("ep_peer"):
+        layer.close()
     torch.save(res, os.path.join(result_dir, f"{mode}{rank}.pt"))
     dist.destroy_process_group()
 
@@ -110,4 +122,4 @@ def test_two_gpu_layer(tmp_path, mode):
             # TP sums two bf16-rounded partial outputs: close to, not identical with, one GPU.
             assert r["vs_single"]["rel_fro"] <= 1e-2, r
             if mode == "tp_peer":
-                assert r["ranks_agree"] and r["second_call"], r
+                assert r["ranks_agree"] and r["second_call"] and r["equals_nccl"], r
