@@ -1,6 +1,6 @@
 """Drop-in for the reference's native module ``electrock_infer._C`` (pytorch_bind.cpp:11-50).
 
-The five MoE ops keep the reference's names, keyword names, in-place output convention
+The ops keep the reference's names, keyword names, in-place output convention
 (everything is caller-allocated, every op returns ``None``) and error type (``RuntimeError``,
 what a failed ``TORCH_CHECK`` surfaces as).  Each forwards raw device pointers to the C-ABI
 library on the current CUDA stream of the tensor's device; nothing is computed in Python.
@@ -254,3 +254,101 @@ def add_rms_norm(input: torch.Tensor, residual: torch.Tensor, epsilon: float,  #
     """``residual <- input + residual`` then ``input <- RMSNorm(residual) * weight``, both in place
     (reference op: pytorch_bind.cpp:60-66; arithmetic of layers/layernorm.py:30-43)."""
     _rms_norm("add_rms_norm", input, residual, epsilon, weight)
+
+
+def paged_store_kvcache(K: torch.Tensor, V: torch.Tensor, K_cache: torch.Tensor,  # noqa: N803
+                        V_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Copies the new tokens' key/value rows into their cache slots
+    (src/store_kv_cache.hip:65-110, pytorch_bind.cpp:92-99; the Triton ``store_kvcache`` of
+    layers/attention_triton_kernel.py:96-106 has the same contract).
+
+    ``K``, ``V`` ``[tokens, kv_heads, head_dim]`` (the token stride may exceed a row, as for
+    slices of a fused QKV projection); caches ``[blocks, block_size, kv_heads, head_dim]``
+    contiguous; ``slot_mapping`` int32 ``[tokens]``, negative entries are skipped.
+    """
+    name = "paged_store_kvcache"
+    for t in (K, V, K_cache, V_cache, slot_mapping):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name}: tensors must be on a CUDA device; there is no CPU implementation")
+    dev = K.device
+    if K.dim() != 3 or V.shape != K.shape:
+        raise RuntimeError(f"{name}: K and V must both be [tokens, kv_heads, head_dim]")
+    num_tokens, kv_heads, head_dim = K.shape
+    if K_cache.dim() != 4 or V_cache.shape != K_cache.shape or tuple(K_cache.shape[2:]) != (kv_heads, head_dim):
+        raise RuntimeError(f"{name}: caches must be [blocks, block_size, {kv_heads}, {head_dim}]")
+    if not (K_cache.is_contiguous() and V_cache.is_contiguous() and slot_mapping.is_contiguous()):
+        raise RuntimeError(f"{name}: caches and slot_mapping must be contiguous")
+    for t in (K, V):
+        if t.stride(2) != 1 or t.stride(1) != head_dim:
+            raise RuntimeError(f"{name}: the heads of a token must be contiguous")
+    if slot_mapping.dtype != torch.int32 or slot_mapping.numel() != num_tokens:
+        raise RuntimeError(f"{name}: slot_mapping must be int32 with one entry per token")
+    if not (K.dtype == V.dtype == K_cache.dtype == V_cache.dtype):
+        raise RuntimeError(f"{name}: K, V and the caches must share a dtype")
+    tag = _float_tag(name, K)
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200moe_paged_store_kvcache(
+            K.data_ptr(), V.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(),
+            slot_mapping.data_ptr(), tag, num_tokens, kv_heads, head_dim,
+            K.stride(0) if num_tokens > 1 else kv_heads * head_dim,
+            V.stride(0) if num_tokens > 1 else kv_heads * head_dim,
+            K_cache.size(0), K_cache.size(1), _stream(dev))
+    _lib.check(rc, name)
+    _lib.count_launches(1)
+
+
+_attn_workspaces: dict = {}
+
+
+def paged_attn_varlen(Q: torch.Tensor, K_cache: torch.Tensor, V_cache: torch.Tensor,  # noqa: N803
+                      max_seqlen_k: int, context_lens: torch.Tensor, block_table: torch.Tensor,
+                      softmax_scale: float, num_splits: int = 0) -> torch.Tensor:
+    """Decode attention of one query token per sequence over the paged cache, grouped-query heads
+    (src/paged_attn_gqa_varlen.hip:216-268, pytorch_bind.cpp:68-77).  Returns a new ``O`` shaped
+    like ``Q [batch, q_heads, 128]``, as the reference does.
+
+    ``max_seqlen_k`` is accepted for signature parity (the reference ignores it; here a positive
+    value only helps to choose ``num_splits``).  Extension: ``num_splits`` (0 = choose) cuts long
+    contexts over several CTAs; block sizes other than 32 are accepted (any multiple of 16).
+    """
+    name = "paged_attn_varlen"
+    dev = _require_cuda(name, Q, K_cache, V_cache, context_lens, block_table)
+    if Q.dim() != 3 or K_cache.dim() != 4 or V_cache.shape != K_cache.shape:
+        raise RuntimeError(f"{name}: Q must be [batch, heads, head_dim] and the caches "
+                           "[blocks, block_size, kv_heads, head_dim]")
+    batch, q_heads, head_dim = Q.shape
+    num_blocks, block_size, kv_heads, cache_dim = K_cache.shape
+    if cache_dim != head_dim:
+        raise RuntimeError(f"{name}: head_dim of Q ({head_dim}) and of the caches ({cache_dim}) differ")
+    if not (Q.dtype == K_cache.dtype == V_cache.dtype):
+        raise RuntimeError(f"{name}: Q and the caches must share a dtype")
+    if context_lens.dtype != torch.int32 or block_table.dtype != torch.int32:
+        raise RuntimeError(f"{name}: context_lens and block_table must be int32")
+    if block_table.dim() != 2 or block_table.size(0) != batch or context_lens.numel() != batch:
+        raise RuntimeError(f"{name}: block_table must be [batch, max_blocks] and context_lens [batch]")
+    tag = _float_tag(name, Q)
+    lib = _lib.load()
+    out = torch.empty_like(Q)
+    max_blocks = block_table.size(1)
+    if num_splits <= 0:
+        longest = max_seqlen_k if max_seqlen_k > 0 else max_blocks * block_size
+        with torch.cuda.device(dev):
+            num_splits = lib.b200moe_paged_attn_num_splits(batch, kv_heads, longest)
+    ws_ptr, ws_bytes = 0, 0
+    if num_splits > 1:
+        ws_bytes = lib.b200moe_paged_attn_workspace_bytes(batch, q_heads, num_splits)
+        key = (dev, _stream(dev))
+        ws = _attn_workspaces.get(key)
+        if ws is None or ws.numel() < ws_bytes:
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            _attn_workspaces[key] = ws
+        ws_ptr = ws.data_ptr()
+    with torch.cuda.device(dev):
+        rc = lib.b200moe_paged_attn_varlen(
+            Q.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), out.data_ptr(),
+            block_table.data_ptr(), context_lens.data_ptr(), tag, batch, q_heads, kv_heads,
+            head_dim, num_blocks, block_size, max_blocks, float(softmax_scale), num_splits,
+            ws_ptr, ws_bytes, _stream(dev))
+    _lib.check(rc, name)
+    _lib.count_launches(2 if num_splits > 1 else 1)
+    return out

@@ -6,7 +6,7 @@ fallback path.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libb200moe.so"
@@ -58,6 +58,14 @@ SIGNATURES = {
                                                    c_int, c_int64, c_int64, c_int, c_void_p]),
     "b200moe_moe_sum_ranks_push": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int64,
                                            c_int64, c_int, c_void_p]),
+    "b200moe_paged_store_kvcache": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                            c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_int,
+                                            c_void_p]),
+    "b200moe_paged_attn_num_splits": (c_int, [c_int, c_int, c_int64]),
+    "b200moe_paged_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "b200moe_paged_attn_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_int,
+                                          c_float, c_int, c_void_p, c_size_t, c_void_p]),
     "b200moe_peer_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
     "b200moe_peer_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "b200moe_peer_close": (c_int, [c_void_p]),

@@ -1,4 +1,5 @@
-"""Bandwidth sweep of the HBM-bound ops (router, alignment, combine, stand-alone SwiGLU).
+"""Bandwidth sweep of the HBM-bound ops (router, alignment, combine, stand-alone SwiGLU, gate
+router, RMSNorm, paged KV-cache store and decode attention).
 
     python -m electrock_infer_b200.opbench [--tokens 1048576 2097152 4194304] [--iters 20]
 
@@ -40,6 +41,7 @@ def main() -> None:
     ap.add_argument("--combine-tokens", type=int, nargs="+", default=[8192, 16384, 65536])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--skip-kv", action="store_true", help="leave out the paged KV-cache ops")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -92,6 +94,34 @@ def main() -> None:
         out = torch.empty(rows, d, dtype=torch.bfloat16, device=dev)
         ms = time_op(lambda: _C.silu_and_mul(out, x), args.iters, flush)
         report("silu_and_mul", rows // 2, rows * d * 2 * 3, ms)
+
+    if args.skip_kv:
+        return
+    # Paged KV cache at Mixtral's head shape (32 query / 8 KV heads of 128), engine block size 256.
+    q_heads, kv_heads, hd, bs = 32, 8, 128, 256
+    for tokens in (8192, 65536):
+        nblk = tokens // bs + 1
+        key = torch.randn(tokens, kv_heads, hd, generator=g, device=dev).to(torch.bfloat16)
+        val = torch.randn(tokens, kv_heads, hd, generator=g, device=dev).to(torch.bfloat16)
+        kc = torch.zeros(nblk, bs, kv_heads, hd, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        slots = torch.randperm(nblk * bs, generator=g, device=dev)[:tokens].to(torch.int32)
+        ms = time_op(lambda: _C.paged_store_kvcache(key, val, kc, vc, slots), args.iters, flush)
+        report("paged_store_kvcache", tokens, tokens * kv_heads * hd * 2 * 4 + tokens * 4, ms)
+    for batch, ctx in ((256, 1024), (256, 4096), (32, 8192), (4, 32768)):
+        per_seq = (ctx + bs - 1) // bs
+        nblk = batch * per_seq
+        kc = torch.randn(nblk, bs, kv_heads, hd, generator=g, device=dev).to(torch.bfloat16)
+        vc = torch.randn(nblk, bs, kv_heads, hd, generator=g, device=dev).to(torch.bfloat16)
+        q = torch.randn(batch, q_heads, hd, generator=g, device=dev).to(torch.bfloat16)
+        table = torch.randperm(nblk, generator=g, device=dev).view(batch, per_seq).to(torch.int32)
+        # Context lengths spread over the upper half of the range, as in a running decode batch.
+        lens = torch.randint(ctx // 2, ctx + 1, (batch,), generator=g, device=dev).to(torch.int32)
+        total = int(lens.sum().item())
+        ms = time_op(lambda: _C.paged_attn_varlen(q, kc, vc, ctx, lens, table, hd ** -0.5),
+                     args.iters, flush)
+        nbytes = total * kv_heads * hd * 2 * 2 + batch * q_heads * hd * 2 * 2
+        report("paged_attn_varlen", total, nbytes, ms, batch=batch, max_context=ctx)
 
 
 if __name__ == "__main__":

@@ -342,6 +342,49 @@ int b200moe_peer_close(void* ptr);
 int b200moe_peer_free(void* ptr);
 
 /*
+ * Paged KV cache: the other custom-kernel family next to the MoE layer in the reference's decoder.
+ *
+ * b200moe_paged_store_kvcache replaces electrock_infer::paged_store_kvcache
+ * (src/store_kv_cache.hip:65-110, pytorch_bind.cpp:92-99) and the Triton store_kvcache the
+ * attention layer calls (layers/attention_triton_kernel.py:75-106, layers/attention.py:33):
+ * token i's key and value rows ([num_kv_heads * head_dim] elements, row strides in elements) are
+ * copied to slot slot_mapping[i] of k_cache / v_cache [num_blocks, block_size, num_kv_heads,
+ * head_dim].  Negative slots are skipped like the reference; slots >= num_blocks * block_size
+ * are skipped too (the reference would write out of bounds).  Any of the three float types.
+ */
+int b200moe_paged_store_kvcache(const void* key, const void* value, void* k_cache, void* v_cache,
+                                const int32_t* slot_mapping, int dtype, int64_t num_tokens,
+                                int num_kv_heads, int head_dim, int64_t key_row_stride,
+                                int64_t value_row_stride, int64_t num_blocks, int block_size,
+                                b200moe_stream_t stream);
+
+/*
+ * b200moe_paged_attn_varlen replaces electrock_infer::paged_attn_varlen
+ * (src/paged_attn_gqa_varlen.hip:216-268, pytorch_bind.cpp:68-77): decode attention of one query
+ * token per sequence over the paged cache, grouped-query heads.
+ *
+ *   q, out [batch, q_heads, 128]; k_cache, v_cache [num_blocks, block_size, kv_heads, 128];
+ *   block_table [batch, max_blocks_per_seq] int32; context_lens [batch] int32.
+ *   out[b, h] = softmax(softmax_scale * q[b, h] . K[b, h / group]) @ V[b, h / group] over the first
+ *   context_lens[b] tokens of sequence b.
+ *
+ * bf16 or fp16, head_dim 128 (as the reference); block_size any multiple of 16 (the reference:
+ * 32 only); up to 16 query heads per KV head.  An empty context gives a zero row (the reference
+ * divides 0 by 0).  num_splits cuts every context into that many ranges handled by separate CTAs
+ * and merged by a second kernel: b200moe_paged_attn_num_splits suggests a value for a batch (1
+ * when the batch alone fills the GPU); num_splits > 1 needs a workspace of
+ * b200moe_paged_attn_workspace_bytes bytes.
+ */
+int b200moe_paged_attn_num_splits(int batch, int kv_heads, int64_t max_context);
+size_t b200moe_paged_attn_workspace_bytes(int batch, int q_heads, int num_splits);
+int b200moe_paged_attn_varlen(const void* q, const void* k_cache, const void* v_cache, void* out,
+                              const int32_t* block_table, const int32_t* context_lens, int dtype,
+                              int batch, int q_heads, int kv_heads, int head_dim,
+                              int64_t num_blocks, int block_size, int max_blocks_per_seq,
+                              float softmax_scale, int num_splits, void* workspace,
+                              size_t workspace_bytes, b200moe_stream_t stream);
+
+/*
  * Device-side status word of the grouped GEMMs.  Their waits on memory barriers are bounded; a
  * wait that runs out records a non-zero code here and the kernel returns.  Reading synchronises
  * with the device.  Returns the code (0 = no error) or a negative B200MOE_ERR_*; `reset` != 0

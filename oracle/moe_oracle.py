@@ -177,6 +177,49 @@ def moe_sum_ranks_ref(x: torch.Tensor) -> torch.Tensor:
     return acc.to(x.dtype)
 
 
+def paged_store_kvcache_ref(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor,
+                            v_cache: torch.Tensor, slot_mapping: torch.Tensor):
+    """Returns copies of the caches ``[blocks, block_size, kv_heads, head_dim]`` with token ``i``'s
+    key/value rows written to slot ``slot_mapping[i]`` (block ``slot // block_size``, offset
+    ``slot % block_size``); negative slots are skipped (src/store_kv_cache.hip:26-31; the torch loop
+    of test/example/test_store_kvcache.py:6-28 is the same copy)."""
+    k_out, v_out = k_cache.detach().cpu().clone(), v_cache.detach().cpu().clone()
+    block_size = k_out.shape[1]
+    for i, slot in enumerate(slot_mapping.detach().cpu().tolist()):
+        if slot < 0:
+            continue
+        k_out[slot // block_size, slot % block_size] = key[i].detach().cpu()
+        v_out[slot // block_size, slot % block_size] = value[i].detach().cpu()
+    return k_out, v_out
+
+
+def paged_attn_varlen_ref(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          context_lens: torch.Tensor, block_table: torch.Tensor,
+                          softmax_scale: float) -> torch.Tensor:
+    """Decode attention over the paged cache in fp32, result cast to the dtype of ``q``: per
+    sequence and query head ``softmax(scale * q K^T) V`` over the first ``context_lens[b]`` tokens,
+    query head ``h`` reading KV head ``h // (q_heads // kv_heads)`` — the arithmetic of the
+    reference's CPU golden (test/example/test_paged_attn.py:24-52), with K and V collected from
+    the pages the block table names instead of taken as contiguous tensors.  An empty context
+    gives a zero row."""
+    q, k_cache, v_cache = q.detach().cpu(), k_cache.detach().cpu(), v_cache.detach().cpu()
+    batch, q_heads, _ = q.shape
+    block_size, kv_heads = k_cache.shape[1], k_cache.shape[2]
+    group = q_heads // kv_heads
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    for b in range(batch):
+        n = int(context_lens[b])
+        if n <= 0:
+            continue
+        pages = block_table[b, : (n + block_size - 1) // block_size].long()
+        k = k_cache[pages].reshape(-1, kv_heads, k_cache.shape[3])[:n].float()
+        v = v_cache[pages].reshape(-1, kv_heads, v_cache.shape[3])[:n].float()
+        for h in range(q_heads):
+            s = (q[b, h].float() @ k[:, h // group].T) * softmax_scale
+            out[b, h] = torch.softmax(s, dim=-1) @ v[:, h // group]
+    return out.to(q.dtype)
+
+
 def rms_norm_ref(x: torch.Tensor, weight: torch.Tensor, eps: float,
                  residual: Optional[torch.Tensor] = None):
     """RMSNorm, optionally after a residual add, as the reference runs it

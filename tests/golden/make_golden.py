@@ -9,6 +9,10 @@ What is run, unmodified, from the reference tree:
   * ``moe_align_block_size_torch``                 test/example/test_align_block.py:6-69
   * ``MixtralSparseMoeBlock``                      test/example/verify_hf_moe.py:43-86
   * ``fused_experts`` with its Triton kernel under ``TRITON_INTERPRET=1`` (fp32 tensors)
+  * ``cpu_attention_golden``                       test/example/test_paged_attn.py:24-52
+  * ``store_kvcache_naive_torch`` and the Triton ``store_kvcache_triton`` (interpreted)
+                                                   test/example/test_store_kvcache.py:6-72
+``--only kv`` regenerates just the KV-cache fixture.
 The reference's compiled module ``electrock_infer._C`` cannot be built here (it targets another
 vendor's compiler), so a stand-in module provides the three ops ``fused_experts`` calls, written
 from the reference's documented formulas (the same functions the oracle exposes).
@@ -84,7 +88,38 @@ def load_reference(ref_root: Path):
     from electrock_infer.layers.moe.softmax_topk import topk_softmax_torch  # noqa: E402
     hf = load("ref_verify_hf_moe", "test/example/verify_hf_moe.py")
     al = load("ref_test_align_block", "test/example/test_align_block.py")
+    load_reference.load = load
     return fused_moe, topk_softmax_torch, hf, al
+
+
+def make_kv() -> None:
+    """Paged KV-cache fixtures: outputs of the reference tests' own CPU goldens on the seeded
+    inputs of tests/kv_cases.py."""
+    sys.path.insert(0, str(REPO / "tests"))
+    import kv_cases
+    pa = load_reference.load("ref_test_paged_attn", "test/example/test_paged_attn.py")
+    sk = load_reference.load("ref_test_store_kvcache", "test/example/test_store_kvcache.py")
+    kv = {}
+    for name in kv_cases.ATTN_CASES:
+        c = kv_cases.attn_case(name)
+        out = pa.cpu_attention_golden(c["q"], c["k"], c["v"], c["context_lens"], c["scale"])
+        mine = moe_oracle.paged_attn_varlen_ref(c["q"], c["k_cache"], c["v_cache"], c["context_lens"],
+                                                c["block_table"], c["scale"])
+        assert torch.equal(out, mine), f"{name}: oracle restatement differs from the reference golden"
+        kv[f"attn_{name}_digest"] = np.array(kv_cases.digest(c["q"], c["k_cache"], c["v_cache"],
+                                                             c["block_table"], c["context_lens"]))
+        kv[f"attn_{name}_out_bits"] = out.view(torch.int16).numpy()
+    c = kv_cases.store_case()
+    k1, v1 = c["k_cache"].clone(), c["v_cache"].clone()
+    sk.store_kvcache_naive_torch(c["key"], c["value"], k1, v1, c["slot_mapping"])
+    k2, v2 = c["k_cache"].clone(), c["v_cache"].clone()
+    sk.store_kvcache_triton(c["key"], c["value"], k2, v2, c["slot_mapping"])  # interpreted on CPU
+    assert torch.equal(k1, k2) and torch.equal(v1, v2), "the reference's two store paths disagree"
+    kv["store_digest"] = np.array(kv_cases.digest(c["key"], c["value"], c["k_cache"], c["v_cache"],
+                                                  c["slot_mapping"]))
+    kv["store_k_bits"] = k1.view(torch.int16).numpy()
+    kv["store_v_bits"] = v1.view(torch.int16).numpy()
+    np.savez_compressed(HERE / "kv.npz", **kv)
 
 
 def run_hf_block(hf, inputs, wl: MoEWorkload, dtype=torch.float32):
@@ -104,8 +139,13 @@ def run_hf_block(hf, inputs, wl: MoEWorkload, dtype=torch.float32):
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--")
+                    else "/root/reference")
     fused_moe, topk_softmax_torch, hf, al = load_reference(ref_root)
+    if "--only" in sys.argv and sys.argv[sys.argv.index("--only") + 1] == "kv":
+        make_kv()
+        print("kv.npz", (HERE / "kv.npz").stat().st_size, "bytes")
+        return
 
     # ------------------------------------------------------------------ router
     router = {}
@@ -183,6 +223,7 @@ def main() -> None:
     ops["moe_sum_in_f16"] = ms.numpy()
     ops["moe_sum_out_f16"] = torch.sum(ms, dim=1).numpy()
     np.savez_compressed(HERE / "ops.npz", **ops)
+    make_kv()
 
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")

@@ -134,3 +134,41 @@ def test_silu_and_moe_sum_formulas(golden):
     assert torch.equal(moe_oracle.moe_sum_ref(ms), torch.from_numpy(g["moe_sum_out_f16"]))
     inter = ms.permute(0, 2, 1).contiguous()
     assert torch.equal(moe_oracle.moe_sum_efficient_ref(inter), torch.from_numpy(g["moe_sum_out_f16"]))
+
+
+# ------------------------------------------------------------------------- paged KV cache
+def _kv_cases():
+    import kv_cases  # tests/kv_cases.py (the tests directory is on sys.path under pytest)
+    return kv_cases
+
+
+@pytest.mark.parametrize("case", ["gqa4_bs32_bf16", "gqa8_bs16_f16", "mha_bs64_bf16", "gqa16_bs256_bf16"])
+def test_paged_attention_oracle_matches_reference_cpu_golden(golden, case):
+    """The fixture holds the output of the reference test's own CPU attention on contiguous K/V;
+    the oracle reads the same K/V through the block table."""
+    kc = _kv_cases()
+    c = kc.attn_case(case)
+    fx = golden["kv"]
+    assert str(fx[f"attn_{case}_digest"]) == kc.digest(c["q"], c["k_cache"], c["v_cache"],
+                                                        c["block_table"], c["context_lens"])
+    out = moe_oracle.paged_attn_varlen_ref(c["q"], c["k_cache"], c["v_cache"], c["context_lens"],
+                                           c["block_table"], c["scale"])
+    assert np.array_equal(out.view(torch.int16).numpy(), fx[f"attn_{case}_out_bits"])
+
+
+def test_paged_store_oracle_matches_reference_torch_and_triton_store(golden):
+    kc = _kv_cases()
+    c = kc.store_case()
+    fx = golden["kv"]
+    assert str(fx["store_digest"]) == kc.digest(c["key"], c["value"], c["k_cache"], c["v_cache"],
+                                                c["slot_mapping"])
+    k, v = moe_oracle.paged_store_kvcache_ref(c["key"], c["value"], c["k_cache"], c["v_cache"],
+                                              c["slot_mapping"])
+    assert np.array_equal(k.view(torch.int16).numpy(), fx["store_k_bits"])
+    assert np.array_equal(v.view(torch.int16).numpy(), fx["store_v_bits"])
+    # Negative slots are skipped (src/store_kv_cache.hip:28-31).
+    slots = c["slot_mapping"].clone()
+    slots[::3] = -1
+    k2, v2 = moe_oracle.paged_store_kvcache_ref(c["key"], c["value"], c["k_cache"], c["v_cache"], slots)
+    untouched = (k2 == 3.0).all(dim=-1).all(dim=-1).sum().item()
+    assert untouched == c["k_cache"].shape[0] * c["k_cache"].shape[1] - int((slots >= 0).sum())
