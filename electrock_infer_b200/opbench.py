@@ -42,6 +42,9 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--skip-kv", action="store_true", help="leave out the paged KV-cache ops")
+    ap.add_argument("--only-kv", action="store_true", help="run only the paged KV-cache ops")
+    ap.add_argument("--kv-cases", nargs="+", default=["256:1024", "256:4096", "32:8192", "4:32768"],
+                    help="decode attention cases as batch:max_context")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -52,7 +55,7 @@ def main() -> None:
         print(json.dumps({"op": op, "tokens": tokens, "algorithmic_bytes": nbytes,
                           "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), **kw}), flush=True)
 
-    for T in args.tokens:
+    for T in ([] if args.only_kv else args.tokens):
         logits = torch.randn(T, 8, generator=g, device=dev)
         w = torch.empty(T, 2, device=dev)
         ids = torch.empty(T, 2, dtype=torch.int32, device=dev)
@@ -70,6 +73,8 @@ def main() -> None:
         report("moe_align_block_size", T, 2 * T * 4 + npp * 4 + (npp // bs) * 4 + 4, ms, launches=3)
 
     H = args.hidden
+    if args.only_kv:
+        args.combine_tokens = []
     for T in args.combine_tokens:
         x = torch.randn(T, 2, H, generator=g, device=dev).to(torch.bfloat16)
         out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
@@ -89,7 +94,7 @@ def main() -> None:
         nw = torch.ones(H, dtype=torch.bfloat16, device=dev)
         ms = time_op(lambda: _C.add_rms_norm(x, res, 1e-5, nw), args.iters, flush)
         report("add_rms_norm", T, T * H * 2 * 4, ms)
-    for rows, d in ((16384, 14336), (4096, 14336)):
+    for rows, d in (() if args.only_kv else ((16384, 14336), (4096, 14336))):
         x = torch.randn(rows, 2 * d, generator=g, device=dev).to(torch.bfloat16)
         out = torch.empty(rows, d, dtype=torch.bfloat16, device=dev)
         ms = time_op(lambda: _C.silu_and_mul(out, x), args.iters, flush)
@@ -108,7 +113,7 @@ def main() -> None:
         slots = torch.randperm(nblk * bs, generator=g, device=dev)[:tokens].to(torch.int32)
         ms = time_op(lambda: _C.paged_store_kvcache(key, val, kc, vc, slots), args.iters, flush)
         report("paged_store_kvcache", tokens, tokens * kv_heads * hd * 2 * 4 + tokens * 4, ms)
-    for batch, ctx in ((256, 1024), (256, 4096), (32, 8192), (4, 32768)):
+    for batch, ctx in (tuple(int(v) for v in c.split(":")) for c in args.kv_cases):
         per_seq = (ctx + bs - 1) // bs
         nblk = batch * per_seq
         kc = torch.randn(nblk, bs, kv_heads, hd, generator=g, device=dev).to(torch.bfloat16)
