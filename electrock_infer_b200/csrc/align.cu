@@ -14,6 +14,8 @@
 // over segments, and a scatter that re-reads the ids (from L2 at these sizes).
 #include <mutex>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -25,6 +27,11 @@ constexpr int kIdsPerWarpStep = 32 * kIdsPerLane;  // 128: a per-expert count fi
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int64_t kSinglePassMax = 8192;
+constexpr int kMaxCluster = 8;                // portable thread-block-cluster size
+// 8 CTAs x 8192 ids.  Above this the three-launch path is faster (measured: 512 Ki ids take 24 us
+// there, while a cluster needs 26 us for 128 Ki and 40 us for 256 Ki: its warps walk their
+// ranges serially).
+constexpr int64_t kClusterPassMax = 65536;
 
 constexpr int kSegThreads = 256;
 constexpr int kSegWarps = kSegThreads / 32;
@@ -136,13 +143,15 @@ __device__ __forceinline__ void warp_scatter(const T* __restrict__ ids, int64_t 
 __device__ __forceinline__ void publish_offsets(const int* total, int num_experts, int block_size,
                                                 int* s_cumsum,
                                                 int32_t* __restrict__ num_tokens_post_pad,
-                                                int32_t* __restrict__ expert_offsets) {
+                                                int32_t* __restrict__ expert_offsets,
+                                                bool write_global = true) {
   int acc = 0;
   s_cumsum[0] = 0;
   for (int x = 0; x < num_experts; ++x) {
     acc += (total[x] + block_size - 1) / block_size * block_size;
     s_cumsum[x + 1] = acc;
   }
+  if (!write_global) return;
   *num_tokens_post_pad = acc;
   if (expert_offsets)
     for (int x = 0; x <= num_experts; ++x) expert_offsets[x] = s_cumsum[x];
@@ -226,6 +235,82 @@ align_single_cta_kernel(const T* __restrict__ ids, int64_t numel, int num_expert
   for (int x = 0; x < kMaxExperts; ++x)
     start[x] = (x < num_experts ? s_cumsum[x] : 0) + s_warp_cnt[warp][x];
   warp_scatter<T>(ids, begin, end, numel, num_experts, lane, start, sorted);
+}
+
+// ---------------------------------------------------------------------------------------------
+// One launch, one thread-block cluster of 2, 4 or 8 CTAs: the single-CTA scheme with the ids cut
+// into one slice per CTA.  The CTAs exchange their per-expert totals through distributed shared
+// memory around a hardware cluster barrier, so no global scratch and no second launch is needed
+// up to kClusterPassMax ids (what a layer call of up to 32 Ki tokens produces).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+align_cluster_kernel(const T* __restrict__ ids, int64_t numel, int num_experts, int block_size,
+                     int32_t* __restrict__ sorted, int64_t sorted_capacity,
+                     int32_t* __restrict__ expert_ids,
+                     int32_t* __restrict__ num_tokens_post_pad,
+                     int32_t* __restrict__ expert_offsets, int fill_pads) {
+  namespace cg = cooperative_groups;
+  __shared__ int s_warp_cnt[kWarps][kMaxExperts];
+  __shared__ int s_cta_total[kMaxExperts];   // read by every CTA of the cluster
+  __shared__ int s_cta_prefix[kMaxExperts];  // ids of each expert in the CTAs before this one
+  __shared__ int s_total[kMaxExperts];
+  __shared__ int s_cumsum[kMaxExperts + 1];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int ncta = static_cast<int>(cluster.num_blocks());
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // Contiguous range per warp over the whole cluster, a multiple of the 128-id warp step.
+  const int64_t steps = ceil_div64(numel, kIdsPerWarpStep);
+  const int64_t per_warp = ceil_div64(steps, static_cast<int64_t>(ncta) * kWarps) * kIdsPerWarpStep;
+  const int64_t begin = min((static_cast<int64_t>(rank) * kWarps + warp) * per_warp, numel);
+  const int64_t end = min(begin + per_warp, numel);
+
+  int cnt[kMaxExperts];
+  warp_count<T>(ids, begin, end, numel, num_experts, lane, cnt);
+  if (lane == 0) {
+#pragma unroll
+    for (int x = 0; x < kMaxExperts; ++x) s_warp_cnt[warp][x] = cnt[x];
+  }
+  __syncthreads();
+  if (threadIdx.x < kMaxExperts) {
+    int acc = 0;
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = s_warp_cnt[w][threadIdx.x];
+      s_warp_cnt[w][threadIdx.x] = acc;
+      acc += c;
+    }
+    s_cta_total[threadIdx.x] = acc;
+  }
+  cluster.sync();  // every CTA's totals are in place
+  if (threadIdx.x < kMaxExperts) {
+    int before = 0, all = 0;
+    for (int r = 0; r < ncta; ++r) {
+      const int c = cluster.map_shared_rank(s_cta_total, r)[threadIdx.x];
+      before += r < rank ? c : 0;
+      all += c;
+    }
+    s_cta_prefix[threadIdx.x] = before;
+    s_total[threadIdx.x] = all;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    publish_offsets(s_total, num_experts, block_size, s_cumsum, num_tokens_post_pad,
+                    expert_offsets, rank == 0);
+  __syncthreads();
+
+  write_blocks_and_pads(s_cumsum, s_total, num_experts, block_size, sorted, sorted_capacity,
+                        expert_ids, fill_pads, rank * kThreads + threadIdx.x, ncta * kThreads);
+
+  int start[kMaxExperts];
+#pragma unroll
+  for (int x = 0; x < kMaxExperts; ++x)
+    start[x] = (x < num_experts ? s_cumsum[x] : 0) + s_cta_prefix[x] + s_warp_cnt[warp][x];
+  warp_scatter<T>(ids, begin, end, numel, num_experts, lane, start, sorted);
+  cluster.sync();  // no CTA leaves while another may still read its totals
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -502,6 +587,26 @@ int run(const void* ids_v, int64_t numel, int E, int bs, int32_t* sorted, int64_
                sorted, cap, expert_ids, npp, offsets, fill);
     return check_launch("moe_align_block_size");
   }
+  if (numel <= kClusterPassMax) {
+    int ncta = 2;
+    while (ncta < kMaxCluster && numel > ncta * kSinglePassMax) ncta *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ncta);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ncta;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaLaunchKernelEx(&cfg, align_cluster_kernel<T>, ids, numel, E, bs, sorted, cap, expert_ids, npp,
+                       offsets, fill);
+    return check_launch("moe_align_block_size");
+  }
   const size_t need = b200moe_align_workspace_bytes(numel, E);
   if (!ws || ws_bytes < need)
     return fail(B200MOE_ERR_WORKSPACE,
@@ -588,12 +693,12 @@ extern "C" int b200moe_align_block_size_noalloc(const void* topk_ids, int ids_dt
 extern "C" size_t b200moe_align_workspace_bytes(int64_t numel, int num_experts) {
   using namespace b200moe;
   (void)num_experts;
-  if (numel <= kSinglePassMax) return 0;
+  if (numel <= kClusterPassMax) return 0;
   const int64_t nseg = ceil_div64(numel, kSegment);
   return static_cast<size_t>(nseg * kMaxExperts + 2 * kMaxExperts + 1) * sizeof(int32_t);
 }
 
-extern "C" int64_t b200moe_align_single_pass_max(void) { return b200moe::kSinglePassMax; }
+extern "C" int64_t b200moe_align_single_pass_max(void) { return b200moe::kClusterPassMax; }
 extern "C" int b200moe_align_max_experts(void) { return b200moe::kMaxExperts; }
 
 extern "C" int b200moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel,

@@ -112,9 +112,10 @@ int b200moe_gate_topk_softmax(const void* hidden_states, const void* gate_weight
  * (layers/moe/moe_align_block_size.py:39-42).  With fill_pads != 0 the kernel itself writes -1
  * to every slot of sorted_token_ids that holds no pair, so no separate fill launch is needed.
  *
- * Inputs longer than b200moe_align_single_pass_max() (8192) need a workspace of
- * b200moe_align_workspace_bytes() bytes (16-byte aligned device memory); shorter inputs run as
- * one launch and ignore it.  num_experts must lie in [1, b200moe_align_max_experts()] (8).
+ * Inputs longer than b200moe_align_single_pass_max() (65536 pair indices) need a workspace of
+ * b200moe_align_workspace_bytes() bytes (16-byte aligned device memory) and take three launches;
+ * shorter inputs run as one launch (one CTA up to 8192 indices, one thread-block cluster of up
+ * to 8 CTAs above that) and ignore it.  num_experts must lie in [1, b200moe_align_max_experts()] (8).
  * Pair indices with an expert outside [0, num_experts) are skipped.
  */
 int b200moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel, int num_experts,

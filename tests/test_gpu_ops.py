@@ -112,7 +112,8 @@ def test_align_golden(golden, case, bs):
 
 
 @pytest.mark.parametrize("numel", [0, 1, 2, 127, 128, 129, 4097, 8191, 8192, 8193, 8300, 16384,
-                                   32768, 65535, 65536, 65537, 70000, 131072, 1000003])
+                                   16385, 32768, 32769, 65535, 65536, 65537, 70000, 131072, 131073,
+                                   200000, 262143, 262144, 262145, 300000, 1000003])
 @pytest.mark.parametrize("fill", [False, True])
 def test_align_sizes(numel, fill):
     rng = np.random.default_rng(numel + 1)
@@ -121,7 +122,7 @@ def test_align_sizes(numel, fill):
 
 
 @pytest.mark.parametrize("dtype", [torch.int64, torch.int16, torch.int8, torch.uint8])
-@pytest.mark.parametrize("numel", [1000, 100000])
+@pytest.mark.parametrize("numel", [1000, 100000, 400000])
 def test_align_id_dtypes(dtype, numel):
     rng = np.random.default_rng(3)
     check_align(rng.integers(0, 8, size=numel), 64, dtype=dtype)
