@@ -1,6 +1,6 @@
 """MoE-layer throughput benchmark: tokens/s of ``FusedMoE.forward`` at Mixtral-8x7B shape.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--parallel tp|tp_nccl|ep]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--parallel ep|ep_nccl|tp|tp_nccl]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...      # the reference's torch CPU path on the host cores
 
@@ -190,9 +190,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--parallel", choices=["tp", "tp_nccl", "ep"], default="ep",
-                    help="N > 1: expert parallel, tensor parallel with the all-reduce inside the "
-                         "layer's kernels (tp), or tensor parallel with NCCL's all-reduce (tp_nccl)")
+    ap.add_argument("--parallel", choices=["tp", "tp_nccl", "ep", "ep_nccl"], default="ep",
+                    help="N > 1: expert parallel over peer memory (ep) or NCCL all-to-alls "
+                         "(ep_nccl), tensor parallel with the all-reduce inside the layer's "
+                         "kernels (tp) or with NCCL's all-reduce (tp_nccl)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--graph", action="store_true",
@@ -245,7 +246,7 @@ def main():
             sys.stdout.flush()
             os.dup2(saved_stdout, 1)
             os.close(saved_stdout)
-    if world > 1 and args.parallel == "ep":
+    if world > 1 and args.parallel in ("ep", "ep_nccl"):
         from electrock_infer_b200.parallel import ExpertParallelMoE
         layer_cls = ExpertParallelMoE
     else:
@@ -268,7 +269,8 @@ def main():
         per = E // world
         inp = make_inputs(wl, device=dev, device_rng=True,
                           expert_slice=slice(rank * per, (rank + 1) * per))
-        layer = layer_cls(E, wl.top_k, H, I, params_dtype=torch.bfloat16).to(dev)
+        layer = layer_cls(E, wl.top_k, H, I, params_dtype=torch.bfloat16,
+                          exchange="nccl" if args.parallel == "ep_nccl" else "auto").to(dev)
         layer.w13_weight.data.copy_(inp["w13"])
         layer.w2_weight.data.copy_(inp["w2"])
         t_loc = T // world

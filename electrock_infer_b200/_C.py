@@ -1,8 +1,8 @@
 """Drop-in for the reference's native module ``electrock_infer._C`` (pytorch_bind.cpp:11-50).
 
-The ops keep the reference's names, keyword names, in-place output convention
-(everything is caller-allocated, every op returns ``None``) and error type (``RuntimeError``,
-what a failed ``TORCH_CHECK`` surfaces as).  Each forwards raw device pointers to the C-ABI
+The ops keep the reference's names, keyword names, output convention (the MoE ops write into
+caller-allocated tensors and return ``None``; ``paged_attn_varlen`` returns a new tensor, as in the
+reference) and error type (``RuntimeError``, what a failed ``TORCH_CHECK`` surfaces as).  Each forwards raw device pointers to the C-ABI
 library on the current CUDA stream of the tensor's device; nothing is computed in Python.
 """
 from __future__ import annotations
@@ -297,6 +297,8 @@ def paged_store_kvcache(K: torch.Tensor, V: torch.Tensor, K_cache: torch.Tensor,
     _lib.count_launches(1)
 
 
+# Split-merge scratch of paged_attn_varlen, kept per (device, stream) so that steady-state calls
+# allocate nothing and calls on different streams never share scratch.
 _attn_workspaces: dict = {}
 
 
@@ -340,6 +342,8 @@ def paged_attn_varlen(Q: torch.Tensor, K_cache: torch.Tensor, V_cache: torch.Ten
         key = (dev, _stream(dev))
         ws = _attn_workspaces.get(key)
         if ws is None or ws.numel() < ws_bytes:
+            if ws is None and len(_attn_workspaces) >= 8:  # bounded: drop the oldest entry
+                _attn_workspaces.pop(next(iter(_attn_workspaces)))
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             _attn_workspaces[key] = ws
         ws_ptr = ws.data_ptr()
