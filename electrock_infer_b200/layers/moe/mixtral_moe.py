@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from .fused_moe import fused_experts
+from .fused_moe import _timed, fused_experts
 
 
 class FusedMoE(nn.Module):
@@ -97,7 +97,8 @@ class FusedMoE(nn.Module):
             gating_output=router_logits, topk=self.top_k, renormalize=self.renormalize,
             inplace=True, activation="silu", tp_reduce=tp_reduce)
         if self.reduce_results and self.tp_size > 1 and tp_reduce is None:
-            dist.all_reduce(final_hidden_states)
+            with _timed("all_reduce:result"):
+                dist.all_reduce(final_hidden_states)
         return final_hidden_states
 
     def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, shard_id: str,
@@ -162,7 +163,8 @@ class MixtralMoE(nn.Module):
                                 self.experts.top_k, renormalize=True, inplace=True,
                                 gate_weight=self.gate.weight, tp_reduce=tp_reduce)
             if self.experts.tp_size > 1 and tp_reduce is None:
-                dist.all_reduce(out)
+                with _timed("all_reduce:result"):
+                    dist.all_reduce(out)
         else:
             out = self.experts(hidden_states, self.gate(hidden_states))
         return out.view(orig_shape)

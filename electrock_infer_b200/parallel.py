@@ -162,7 +162,8 @@ class TensorParallelReduce:
     def finish(self, st: dict, output: torch.Tensor, top_k: int) -> None:
         """Everything after the second GEMM: barrier, combine + push, barrier, copy."""
         num_tokens, hidden = output.shape
-        dist.all_reduce(st["token"], group=self.group)
+        with _timed("barrier:gemm2_done"):
+            dist.all_reduce(st["token"], group=self.group)
         with _timed("moe_sum_ranks_push"):
             _lib.check(_lib.load().b200moe_moe_sum_ranks_push(
                 st["recv"].local.data_ptr(), st["out"].table.data_ptr(), self.world,
@@ -170,8 +171,10 @@ class TensorParallelReduce:
                 st["tokens_per_rank"], hidden, top_k,
                 torch.cuda.current_stream(output.device).cuda_stream), "moe_sum_ranks_push")
         _lib.count_launches(1)
-        dist.all_reduce(st["token"], group=self.group)
-        output.copy_(st["out_local"])
+        with _timed("barrier:rows_landed"):
+            dist.all_reduce(st["token"], group=self.group)
+        with _timed("copy:result"):
+            output.copy_(st["out_local"])
 
 
 class CudaOps:
@@ -398,10 +401,12 @@ class ExpertParallelMoE(nn.Module):
         dev = hidden_states.device
         cap = st["capacity"]
         weights, ids = self.ops.route(router_logits, k, self.renormalize)
-        st["x_local"].copy_(hidden_states)
+        with _timed("copy:stage_tokens"):
+            st["x_local"].copy_(hidden_states)
         # The all-gathers also order every rank's staging copy before any rank's gather.
-        dist.all_gather_into_tensor(st["ids_all"], ids.view(-1), group=self.group)
-        dist.all_gather_into_tensor(st["w_all"], weights.view(-1), group=self.group)
+        with _timed("all_gather:ids_weights"):
+            dist.all_gather_into_tensor(st["ids_all"], ids.view(-1), group=self.group)
+            dist.all_gather_into_tensor(st["w_all"], weights.view(-1), group=self.group)
         local_ids = st["ids_all"] - self.first_expert  # other ranks' experts fall outside [0, per)
         stream = torch.cuda.current_stream(dev).cuda_stream
         with _timed("moe_align_block_size"):
@@ -426,7 +431,8 @@ class ExpertParallelMoE(nn.Module):
         _lib.count_launches(3)
         # Every rank's second GEMM (whose epilogue wrote into this rank's buffer) has finished once
         # this one-word all-reduce completes.
-        dist.all_reduce(st["token"], group=self.group)
+        with _timed("barrier:gemm2_done"):
+            dist.all_reduce(st["token"], group=self.group)
         with _timed("moe_sum"):
             _C.moe_sum(st["c3_local"], hidden_states)
         return hidden_states
