@@ -292,16 +292,25 @@ class ExpertParallelMoE(nn.Module):
     ``FusedMoE`` (experts that live elsewhere are ignored by the loader).
     ``forward(hidden_states [T_local, H], router_logits [T_local, E])`` overwrites and returns
     ``hidden_states``.
+
+    The peer-memory exchange is used when every rank holds the same number of tokens, or, with
+    ``max_tokens_per_rank`` set, for ANY token counts up to that bound (ragged batches, ranks with
+    no tokens at all): buffers are sized for the bound once, shorter batches are padded with pair
+    indices the alignment skips, and no step synchronises with the host.  Every rank must then
+    stay within the bound.
     """
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
                  params_dtype: Optional[torch.dtype] = None, renormalize: bool = True,
                  group: Optional[dist.ProcessGroup] = None, ops=None,
-                 exchange: str = "auto"):
+                 exchange: str = "auto", max_tokens_per_rank: Optional[int] = None):
         super().__init__()
         if exchange not in ("auto", "peer", "nccl"):
             raise ValueError("exchange must be 'auto', 'peer' or 'nccl'")
+        if max_tokens_per_rank is not None and max_tokens_per_rank < 1:
+            raise ValueError("max_tokens_per_rank must be positive")
         self.exchange = exchange
+        self.max_tokens_per_rank = max_tokens_per_rank
         self._peer_states = {}
         self.group = group
         self.ep_size = dist.get_world_size(group)
@@ -351,26 +360,35 @@ class ExpertParallelMoE(nn.Module):
 
     # ------------------------------------------------------------------ peer-memory exchange
     def _peer_state(self, num_tokens: int, hidden: int, device: torch.device):
-        """Buffers of the peer-memory path for batches of ``num_tokens`` tokens per rank, or None
-        when the ranks do not all hold that many tokens (set-up: allocates and synchronises)."""
-        key = (num_tokens, hidden, device)
+        """Buffers of the peer-memory path, or None when it does not apply (set-up: allocates and
+        synchronises the first time).  With ``max_tokens_per_rank`` the buffers hold that many
+        tokens per rank; otherwise every rank must hold exactly ``num_tokens`` tokens."""
+        bounded = self.max_tokens_per_rank is not None
+        cap_tokens = self.max_tokens_per_rank if bounded else num_tokens
+        key = (cap_tokens, bounded, hidden, device)
         if key in self._peer_states:
             return self._peer_states[key]
-        counts = [None] * self.ep_size
-        dist.all_gather_object(counts, num_tokens, group=self.group)
+        usable = cap_tokens > 0
+        if not bounded:
+            counts = [None] * self.ep_size
+            dist.all_gather_object(counts, num_tokens, group=self.group)
+            usable = usable and all(c == num_tokens for c in counts)
         state = None
-        if all(c == num_tokens for c in counts) and num_tokens > 0:
+        if usable:
             ep, k, per = self.ep_size, self.top_k, self.experts_per_rank
-            pairs_total = ep * num_tokens * k
+            pairs_total = ep * cap_tokens * k
             cap = pairs_total + per * (BLOCK_SIZE_M - 1)
             i32 = dict(dtype=torch.int32, device=device)
             bf16 = dict(dtype=torch.bfloat16, device=device)
-            x_stage = PeerBuffer(num_tokens * hidden * 2, device, self.group)
-            cache3 = PeerBuffer(num_tokens * k * hidden * 2, device, self.group)
+            x_stage = PeerBuffer(cap_tokens * hidden * 2, device, self.group)
+            cache3 = PeerBuffer(cap_tokens * k * hidden * 2, device, self.group)
             state = {
-                "x_stage": x_stage, "cache3": cache3, "capacity": cap,
-                "x_local": x_stage.local.view(torch.bfloat16).view(num_tokens, hidden),
-                "c3_local": cache3.local.view(torch.bfloat16).view(num_tokens, k, hidden),
+                "x_stage": x_stage, "cache3": cache3, "capacity": cap, "cap_tokens": cap_tokens,
+                "x_local": x_stage.local.view(torch.bfloat16).view(cap_tokens, hidden),
+                "c3_local": cache3.local.view(torch.bfloat16).view(cap_tokens, k, hidden),
+                # Own ids and weights padded to cap_tokens rows; -1 never matches an expert.
+                "ids_pad": torch.full((cap_tokens * k,), -1, **i32),
+                "w_pad": torch.zeros(cap_tokens * k, dtype=torch.float32, device=device),
                 "ids_all": torch.empty(pairs_total, **i32),
                 "w_all": torch.empty(pairs_total, dtype=torch.float32, device=device),
                 "sorted_ids": torch.empty(cap, **i32),
@@ -399,14 +417,24 @@ class ExpertParallelMoE(nn.Module):
         ep, per, k = self.ep_size, self.experts_per_rank, self.top_k
         num_tokens, hidden = hidden_states.shape
         dev = hidden_states.device
-        cap = st["capacity"]
+        cap, cap_tokens = st["capacity"], st["cap_tokens"]
+        if num_tokens > cap_tokens:
+            raise RuntimeError(f"ExpertParallelMoE: {num_tokens} tokens exceed max_tokens_per_rank="
+                               f"{cap_tokens}")
         weights, ids = self.ops.route(router_logits, k, self.renormalize)
         with _timed("copy:stage_tokens"):
-            st["x_local"].copy_(hidden_states)
+            st["x_local"][:num_tokens].copy_(hidden_states)
+        if num_tokens == cap_tokens:
+            ids_own, w_own = ids.view(-1), weights.view(-1)
+        else:  # a short batch: rows past num_tokens carry pair indices the alignment skips
+            ids_own, w_own = st["ids_pad"], st["w_pad"]
+            ids_own.fill_(-1)
+            ids_own[: num_tokens * k].copy_(ids.view(-1))
+            w_own[: num_tokens * k].copy_(weights.view(-1))
         # The all-gathers also order every rank's staging copy before any rank's gather.
         with _timed("all_gather:ids_weights"):
-            dist.all_gather_into_tensor(st["ids_all"], ids.view(-1), group=self.group)
-            dist.all_gather_into_tensor(st["w_all"], weights.view(-1), group=self.group)
+            dist.all_gather_into_tensor(st["ids_all"], ids_own, group=self.group)
+            dist.all_gather_into_tensor(st["w_all"], w_own, group=self.group)
         local_ids = st["ids_all"] - self.first_expert  # other ranks' experts fall outside [0, per)
         stream = torch.cuda.current_stream(dev).cuda_stream
         with _timed("moe_align_block_size"):
@@ -414,7 +442,7 @@ class ExpertParallelMoE(nn.Module):
                                     st["num_post_pad"], fill_pads=True, workspace=st["align_ws"])
         with _timed("gather_rows"):
             _lib.check(lib.b200moe_gather_rows_peer(
-                st["x_stage"].table.data_ptr(), ep, num_tokens, st["a_sorted"].data_ptr(),
+                st["x_stage"].table.data_ptr(), ep, cap_tokens, st["a_sorted"].data_ptr(),
                 st["sorted_ids"].data_ptr(), st["num_post_pad"].data_ptr(), cap, hidden, k, stream),
                 "gather_rows_peer")
         with _timed("grouped_gemm_w13_swiglu"):
@@ -425,7 +453,7 @@ class ExpertParallelMoE(nn.Module):
         with _timed("grouped_gemm_w2_scale"):
             _lib.check(lib.b200moe_grouped_gemm_w2_scale_peer(
                 st["act"].data_ptr(), self.w2_weight.data_ptr(), st["cache3"].table.data_ptr(), ep,
-                num_tokens * k, st["w_all"].data_ptr(), st["sorted_ids"].data_ptr(),
+                cap_tokens * k, st["w_all"].data_ptr(), st["sorted_ids"].data_ptr(),
                 st["expert_ids"].data_ptr(), st["num_post_pad"].data_ptr(), cap, per, hidden,
                 self.intermediate_size, BLOCK_SIZE_M, stream), "grouped_gemm_w2_scale_peer")
         _lib.count_launches(3)
@@ -434,7 +462,7 @@ class ExpertParallelMoE(nn.Module):
         with _timed("barrier:gemm2_done"):
             dist.all_reduce(st["token"], group=self.group)
         with _timed("moe_sum"):
-            _C.moe_sum(st["c3_local"], hidden_states)
+            _C.moe_sum(st["c3_local"][:num_tokens], hidden_states)
         return hidden_states
 
     def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:

@@ -450,3 +450,46 @@ def test_layer_mixtral_prefill_shape_sampled():
     outh = fused_experts(xh, inp["w13"].to(DEV), inp["w2"].to(DEV), inp["logits"][:half].to(DEV), 2,
                          inplace=True)
     assert torch.equal(outh, full[:half])
+
+
+def test_expert_parallel_peer_path_with_one_rank_and_ragged_batches():
+    """The peer-memory exchange of ExpertParallelMoE in a process group of one rank: the same
+    kernels and buffers as on several GPUs (the peer tables just hold one entry).  With a bound on
+    the tokens per rank, batches shorter than the bound (and an empty one) are padded with pair
+    indices the alignment skips; results must equal the plain layer bit for bit."""
+    import socket
+
+    import torch.distributed as dist
+
+    from electrock_infer_b200.parallel import ExpertParallelMoE
+    if dist.is_initialized():
+        pytest.skip("a process group is already initialised in this process")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    dev = torch.device(DEV)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                            device_id=dev)
+    try:
+        wl = MoEWorkload("ep1", 400, 512, 1024, seed=77, logit_bias=(1, 1, 0, 0, 0, 0, -1, -1))
+        inp = make_inputs(wl)
+        w13, w2 = inp["w13"].to(dev), inp["w2"].to(dev)
+        single = fused_experts(inp["x"].to(dev), w13, w2, inp["logits"].to(dev), 2, inplace=False)
+        layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
+                                  exchange="peer", max_tokens_per_rank=400).to(dev)
+        layer.w13_weight.data.copy_(w13)
+        layer.w2_weight.data.copy_(w2)
+        for lo, hi in ((0, 400), (13, 350), (0, 0), (363, 400)):
+            x = inp["x"][lo:hi].to(dev).clone()
+            out = layer(x, inp["logits"][lo:hi].to(dev))
+            torch.cuda.synchronize()
+            assert out.data_ptr() == x.data_ptr() and out.shape[0] == hi - lo
+            assert torch.equal(out, single[lo:hi]), (lo, hi)
+        with pytest.raises(RuntimeError, match="max_tokens_per_rank"):
+            layer(torch.zeros(401, wl.hidden, dtype=torch.bfloat16, device=dev),
+                  torch.zeros(401, 8, device=dev))
+        assert gemm_status() == 0
+        layer.close()
+    finally:
+        dist.destroy_process_group()

@@ -73,6 +73,27 @@ def _worker(rank, port, mode, result_dir):
             out3 = layer(full["x"].to(dev).clone(), full["logits"].to(dev))
             torch.cuda.synchronize()
             res["equals_nccl"] = bool(torch.equal(out3, out))
+    elif mode == "ep_peer_ragged":
+        # Peer-memory exchange with a per-rank bound: uneven token counts, then a rank with no
+        # tokens at all, with no host synchronisation in either step.
+        layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
+                                  exchange="peer", max_tokens_per_rank=400).to(dev)
+        for e in range(8):
+            layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
+            layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
+            layer.weight_loader(layer.w2_weight, full["w2"][e].to(dev), "w2", e)
+        lo, hi = (0, 350) if rank == 0 else (350, 600)
+        x = full["x"][lo:hi].to(dev).clone()
+        out = layer(x, full["logits"][lo:hi].to(dev))
+        torch.cuda.synchronize()
+        res["alias"] = out.data_ptr() == x.data_ptr()
+        res["stats"] = moe_oracle.error_stats(out.cpu().float(), want[lo:hi])
+        res["bit_exact_vs_single"] = bool(torch.equal(out, single[lo:hi]))
+        lo, hi = (0, 0) if rank == 0 else (563, 600)      # rank 0 sits this step out
+        x2 = full["x"][lo:hi].to(dev).clone()
+        out2 = layer(x2, full["logits"][lo:hi].to(dev))
+        torch.cuda.synchronize()
+        res["bit_exact_second_call"] = bool(torch.equal(out2, single[lo:hi])) and out2.shape[0] == hi - lo
     else:
         layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
                                   exchange="peer" if mode.startswith("ep_peer") else "nccl").to(dev)
@@ -106,7 +127,7 @@ def _worker(rank, port, mode, result_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["tp", "tp_peer", "ep", "ep_peer", "ep_peer_tiny"])
+@pytest.mark.parametrize("mode", ["tp", "tp_peer", "ep", "ep_peer", "ep_peer_tiny", "ep_peer_ragged"])
 def test_two_gpu_layer(tmp_path, mode):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
