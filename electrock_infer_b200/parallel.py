@@ -1,8 +1,9 @@
 """Sharding the MoE layer over the GPUs of one NVLink/NVSwitch box with ``torch.distributed``.
 
 Tensor parallel is what the reference does: ``FusedMoE(tp_size=world, reduce_results=True)`` shards
-the intermediate dimension and all-reduces the combined output (layers/moe/mixtral_moe.py:114-116);
-nothing more is needed for it than the class in ``layers.moe``.
+the intermediate dimension and all-reduces the combined output (layers/moe/mixtral_moe.py:114-116).
+The class in ``layers.moe`` does that with NCCL, or, through :class:`TensorParallelReduce` below,
+inside the layer's own kernels over NVLink peer mappings.
 
 Expert parallel has no counterpart in the reference (its docstring says EP was removed,
 layers/moe/mixtral_moe.py:9-13).  ``ExpertParallelMoE`` keeps ``num_experts / world`` whole experts
@@ -18,8 +19,9 @@ touches them.  Every arithmetic step is the one the single-GPU layer performs on
 the result is bit-identical to the single-GPU result for the same tokens.
 
 That exchange needs the split sizes on the host, i.e. one device synchronisation per call.  When
-every rank holds the same number of tokens, ``ExpertParallelMoE`` instead moves the rows inside
-its own kernels over NVLink peer mappings and never synchronises with the host:
+every rank holds the same number of tokens, or a bound on the tokens per rank is given,
+``ExpertParallelMoE`` instead moves the rows inside its own kernels over NVLink peer mappings and
+never synchronises with the host:
 
     route locally -> copy the tokens into a peer-visible staging buffer
     -> all-gather the (tiny) expert ids and routing weights
