@@ -12,8 +12,9 @@
 // 128 rows x 256 accumulator columns; for w13 the 256 columns are 128 gate columns followed by
 // the 128 matching up columns, fetched as two TMA boxes of the unmodified [E, 2*inter, hidden]
 // parameter, so that SiLU(g)*u is formed inside one thread without any exchange.  Tiles are
-// numbered expert-major, then N tile, then M block (M fastest): CTAs running side by side share
-// a weight tile through L2 while the expert's activation rows stay L2-resident.
+// numbered expert-major, then by groups of M blocks whose activation rows fit a share of L2,
+// then N tile, then M block (M fastest): CTAs running side by side share a weight tile through
+// L2 while the group's activation rows stay L2-resident.
 //
 // CTA layout (192 threads, one CTA per SM, grid = number of SMs):
 //   warp 0      TMA producer (one lane)         smem ring of kStages x (A 16 KiB + B 32 KiB)
