@@ -85,9 +85,19 @@ class FusedMoE(nn.Module):
                                    "and a token count divisible by tp_size")
         elif not applies or num_tokens * hidden * hidden_states.element_size() < self.PEER_REDUCE_MIN_BYTES:
             return None
+        from ...parallel import PeerMemoryUnavailable, TensorParallelReduce
         if self._tp_reduce is None:
-            from ...parallel import TensorParallelReduce
             self._tp_reduce = TensorParallelReduce()
+        try:  # set-up on first use; fails on every rank alike when peer mappings are not possible
+            self._tp_reduce.state(num_tokens, self.top_k, hidden, hidden_states.device)
+        except PeerMemoryUnavailable as e:
+            if self.tp_exchange == "peer":
+                raise
+            import warnings
+            warnings.warn(f"FusedMoE: in-kernel tensor-parallel reduce unavailable ({e}); "
+                          "using the NCCL all-reduce")
+            self.tp_exchange = "nccl"
+            return None
         return self._tp_reduce
 
     def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:

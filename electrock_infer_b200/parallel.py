@@ -54,12 +54,21 @@ class _RawDeviceMemory:
                                          "version": 3, "strides": None}
 
 
+class PeerMemoryUnavailable(RuntimeError):
+    """Raised on EVERY rank of the group when any rank could not allocate or map a peer-visible
+    buffer (no peer access between the GPUs, CUDA IPC not permitted, out of memory)."""
+
+
 class PeerBuffer:
     """A device buffer that every rank of ``group`` (all on one node) can address: a cudaMalloc
     allocation per rank, shared with CUDA IPC handles.  ``table`` is a device int64 tensor holding
     the address of every rank's buffer as seen from this process (own buffer: the local address);
     ``local`` is a uint8 torch view of the own buffer.  Creating one is a set-up step (it
-    allocates, synchronises and exchanges handles through the process group)."""
+    allocates, synchronises and exchanges handles through the process group).
+
+    Construction is collective and fails collectively: the ranks compare notes before anyone uses
+    the buffers, and if one of them failed, all of them release what they hold and raise
+    :class:`PeerMemoryUnavailable`, so that callers can fall back to NCCL on every rank alike."""
 
     def __init__(self, nbytes: int, device: torch.device, group=None):
         import ctypes
@@ -71,19 +80,37 @@ class PeerBuffer:
         world = dist.get_world_size(group)
         own = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
+        error = None
+        mapped_ptrs = {}
         with torch.cuda.device(device):
-            _lib.check(lib.b200moe_peer_alloc(nbytes, ctypes.byref(own), handle), "peer_alloc")
+            if lib.b200moe_peer_alloc(nbytes, ctypes.byref(own), handle) != 0:
+                error = "peer_alloc: " + lib.b200moe_last_error().decode(errors="replace")
             handles = [None] * world
-            dist.all_gather_object(handles, handle.raw, group=group)
-            self.ptrs = []
-            for r in range(world):
-                if r == self.rank:
-                    self.ptrs.append(own.value)
-                else:
+            dist.all_gather_object(handles, None if error else handle.raw, group=group)
+            if error is None and any(h is None for h in handles):
+                error = "another rank could not allocate its buffer"
+            if error is None:
+                for r in range(world):
+                    if r == self.rank:
+                        continue
                     mapped = ctypes.c_void_p()
                     buf = ctypes.create_string_buffer(handles[r], 64)
-                    _lib.check(lib.b200moe_peer_open(buf, ctypes.byref(mapped)), "peer_open")
-                    self.ptrs.append(mapped.value)
+                    if lib.b200moe_peer_open(buf, ctypes.byref(mapped)) != 0:
+                        error = f"peer_open (rank {r}): " + lib.b200moe_last_error().decode(errors="replace")
+                        break
+                    mapped_ptrs[r] = mapped.value
+            errors = [None] * world
+            dist.all_gather_object(errors, error, group=group)
+            if any(e is not None for e in errors):
+                for ptr in mapped_ptrs.values():
+                    lib.b200moe_peer_close(ptr)
+                dist.barrier(group=group)  # nobody frees a buffer another rank still maps
+                if own.value:
+                    lib.b200moe_peer_free(own.value)
+                self.ptrs = []
+                raise PeerMemoryUnavailable("; ".join(
+                    f"rank {r}: {e}" for r, e in enumerate(errors) if e is not None))
+        self.ptrs = [own.value if r == self.rank else mapped_ptrs[r] for r in range(world)]
         self.table = torch.tensor(self.ptrs, dtype=torch.int64, device=device)
         self.local = torch.as_tensor(_RawDeviceMemory(own.value, nbytes), device=device)
 
@@ -141,7 +168,11 @@ class TensorParallelReduce:
             per = num_tokens // self.world
             slot_bytes = per * top_k * hidden * 2
             recv = PeerBuffer(self.world * slot_bytes, device, self.group)
-            out = PeerBuffer(num_tokens * hidden * 2, device, self.group)
+            try:
+                out = PeerBuffer(num_tokens * hidden * 2, device, self.group)
+            except PeerMemoryUnavailable:
+                recv.close()
+                raise
             st = {
                 "recv": recv, "out": out, "tokens_per_rank": per,
                 # Where this rank's rows go in every rank's receive buffer.
@@ -382,8 +413,24 @@ class ExpertParallelMoE(nn.Module):
             cap = pairs_total + per * (BLOCK_SIZE_M - 1)
             i32 = dict(dtype=torch.int32, device=device)
             bf16 = dict(dtype=torch.bfloat16, device=device)
-            x_stage = PeerBuffer(cap_tokens * hidden * 2, device, self.group)
-            cache3 = PeerBuffer(cap_tokens * k * hidden * 2, device, self.group)
+            try:
+                x_stage = PeerBuffer(cap_tokens * hidden * 2, device, self.group)
+                try:
+                    cache3 = PeerBuffer(cap_tokens * k * hidden * 2, device, self.group)
+                except PeerMemoryUnavailable:
+                    x_stage.close()
+                    raise
+            except PeerMemoryUnavailable as e:
+                # Every rank lands here together.  Forced peer mode has no other way; otherwise
+                # the NCCL exchange takes over for good.
+                if self.exchange == "peer":
+                    raise
+                import warnings
+                warnings.warn(f"ExpertParallelMoE: peer-memory exchange unavailable ({e}); "
+                              "using NCCL all-to-alls")
+                self.exchange = "nccl"
+                self._peer_states[key] = None
+                return None
             state = {
                 "x_stage": x_stage, "cache3": cache3, "capacity": cap, "cap_tokens": cap_tokens,
                 "x_local": x_stage.local.view(torch.bfloat16).view(cap_tokens, hidden),

@@ -43,11 +43,15 @@ def _worker(rank, port, mode, result_dir):
     single = fused_experts(full["x"].to(dev), full["w13"].to(dev), full["w2"].to(dev),
                            full["logits"].to(dev), 2, inplace=False)
     res = {}
+    if mode.endswith("_fallback") and rank == 1:
+        # One rank cannot map its peers' buffers: every rank must notice and use NCCL instead.
+        _lib.load().b200moe_peer_open = lambda *args: -6
     if mode.startswith("tp"):
         # "tp": the reference's NCCL all-reduce; "tp_peer": the all-reduce inside the layer's kernels.
         layer = FusedMoE(8, 2, wl.hidden, wl.inter, tp_size=WORLD, params_dtype=torch.bfloat16,
                          reduce_results=True,
-                         tp_exchange="peer" if mode == "tp_peer" else "nccl").to(dev)
+                         tp_exchange={"tp_peer": "peer", "tp_auto_fallback": "auto"}.get(mode, "nccl")).to(dev)
+        layer.PEER_REDUCE_MIN_BYTES = 0   # "auto" would otherwise keep NCCL for this small batch
         for e in range(8):
             layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
             layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
@@ -58,6 +62,8 @@ def _worker(rank, port, mode, result_dir):
         res["alias"] = out.data_ptr() == x.data_ptr()
         res["stats"] = moe_oracle.error_stats(out.cpu().float(), want)
         res["vs_single"] = moe_oracle.error_stats(out.cpu().float(), single.cpu().float())
+        if mode == "tp_auto_fallback":
+            res["fell_back"] = layer.tp_exchange == "nccl"
         if mode == "tp_peer":
             # Every rank must hold the same bits, and a second call must reuse the buffers cleanly.
             both = [torch.empty_like(out) for _ in range(WORLD)]
@@ -96,12 +102,13 @@ def _worker(rank, port, mode, result_dir):
         res["bit_exact_second_call"] = bool(torch.equal(out2, single[lo:hi])) and out2.shape[0] == hi - lo
     else:
         layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
-                                  exchange="peer" if mode.startswith("ep_peer") else "nccl").to(dev)
+                                  exchange="peer" if mode.startswith("ep_peer") else
+                                  ("auto" if mode == "ep_auto_fallback" else "nccl")).to(dev)
         for e in range(8):
             layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
             layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)
             layer.weight_loader(layer.w2_weight, full["w2"][e].to(dev), "w2", e)
-        if mode.startswith("ep_peer"):  # the peer-memory exchange needs equal splits
+        if mode.startswith("ep_peer") or mode == "ep_auto_fallback":  # equal splits: "auto" tries peer memory
             lo, hi = (0, tokens // 2) if rank == 0 else (tokens // 2, tokens)
         else:
             lo, hi = (0, 350) if rank == 0 else (350, 600)  # uneven token split
@@ -116,6 +123,8 @@ def _worker(rank, port, mode, result_dir):
         out2 = layer(x2, full["logits"][lo:hi].to(dev).flip(0).contiguous())
         torch.cuda.synchronize()
         res["bit_exact_second_call"] = bool(torch.equal(out2, single[lo:hi].flip(0)))
+        if mode == "ep_auto_fallback":
+            res["fell_back"] = layer.exchange == "nccl"
     res["gemm_status"] = _lib.load().b200moe_gemm_device_status(1)
     # Release the peer-visible buffers once every rank has finished with them.
     dist.barrier()
@@ -127,7 +136,8 @@ def _worker(rank, port, mode, result_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["tp", "tp_peer", "ep", "ep_peer", "ep_peer_tiny", "ep_peer_ragged"])
+@pytest.mark.parametrize("mode", ["tp", "tp_peer", "tp_auto_fallback", "ep", "ep_peer", "ep_peer_tiny",
+                                  "ep_peer_ragged", "ep_auto_fallback"])
 def test_two_gpu_layer(tmp_path, mode):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
@@ -136,6 +146,8 @@ def test_two_gpu_layer(tmp_path, mode):
         r = torch.load(tmp_path / f"{mode}{rank}.pt")
         assert r["alias"] and r["gemm_status"] == 0, r
         assert r["stats"]["max_abs"] <= 3e-2 and r["stats"]["rel_fro"] <= 1e-2, r
+        if mode.endswith("_fallback"):
+            assert r["fell_back"], "every rank must have switched to NCCL"
         if mode.startswith("ep"):
             assert r["bit_exact_vs_single"], "expert-parallel rows must equal the single-GPU rows"
             assert r["bit_exact_second_call"]
