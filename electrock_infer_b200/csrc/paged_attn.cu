@@ -361,11 +361,13 @@ int launch(const Params& p, int batch, cudaStream_t st) {
 extern "C" int b200moe_paged_attn_num_splits(int batch, int kv_heads, int64_t max_context) {
   using namespace b200moe;
   if (batch < 1 || kv_heads < 1 || max_context < 1) return 1;
-  // Fill, but do not exceed, one wave of two CTAs per SM (a few CTAs spilling into a second wave
-  // would double the time); a split should still cover a few hundred tokens.
+  // Two CTAs fit an SM.  Aim for about three waves of CTAs, so that the partial last wave costs
+  // little, as long as a split still covers 512 tokens or more (measured on B200: 48 sequences
+  // x 8 KV heads x 4096 tokens take 133-142 us unsplit and 121 us in 3 splits; 16 x 8 x 8192
+  // take 100 us in 2 splits and 89 us in 7).
   const int64_t ctas = static_cast<int64_t>(batch) * kv_heads;
-  const int64_t want = 2ll * sm_count() / ctas;
-  const int64_t by_length = max_context / 256 > 0 ? max_context / 256 : 1;
+  const int64_t want = ceil_div64(6ll * sm_count(), ctas);
+  const int64_t by_length = max_context / 512 > 0 ? max_context / 512 : 1;
   int64_t s = want < by_length ? want : by_length;
   if (s < 1) s = 1;
   if (s > 64) s = 64;
