@@ -134,8 +134,13 @@ def _tp_worker(rank, port, result_dir):
         refused = False
     except RuntimeError:
         refused = True
+    # Token-slice ownership of the in-kernel reduce: only whole slices, never an empty batch.
+    from electrock_infer_b200.parallel import TensorParallelReduce
+    red = TensorParallelReduce()
+    slices_ok = (red.world == WORLD and red.rank == rank and red.usable(600) and not red.usable(601)
+                 and not red.usable(0))
     torch.save({"err": (out - want).abs().max().item(), "alias": out.data_ptr() == x.data_ptr(),
-                "refused": refused},
+                "refused": refused and slices_ok},
                os.path.join(result_dir, f"tp{rank}.pt"))
     dist.destroy_process_group()
 
