@@ -71,6 +71,7 @@ SIGNATURES = {
     "b200moe_peer_close": (c_int, [c_void_p]),
     "b200moe_peer_free": (c_int, [c_void_p]),
     "b200moe_gemm_device_status": (c_int, [c_int]),
+    "b200moe_gemm_set_tiling": (c_int, [c_int]),
 }
 
 _lib = None

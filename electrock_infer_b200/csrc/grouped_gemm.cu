@@ -21,6 +21,8 @@
 //   warp 1      tcgen05.mma issuer (one lane)   owns the TMEM allocation (512 columns = 2 tiles)
 //   warps 2..5  epilogue: tcgen05.ld -> math -> per-warp smem staging -> 128-byte row stores
 // Two TMEM accumulators let the epilogue of tile i overlap the MMAs of tile i+1.
+// Variants further down: two M blocks per tile sharing each weight stage (grouped_gemm_dual_kernel,
+// chosen for long batches) and CTA pairs with tcgen05 cta_group::2 (grouped_gemm_pair_kernel).
 //
 // Every mbarrier wait is bounded (about a second of SM clocks).  A wait that runs out sets the
 // CTA's abort flag and a device status word, every role leaves its loop, TMEM is released and the
@@ -28,6 +30,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -286,6 +289,144 @@ struct GemmParams {
   int num_src_rows;              // kW13Gather: rows of the token tensor
 };
 
+
+// ------------------------------------------------------------------------------ epilogue bodies
+// One epilogue warp drains its 32 rows (TMEM lanes 32*quarter ..) of one 128-row accumulator.
+// `taddr` addresses the warp's lanes at the accumulator's first column; `stage_out` is the warp's
+// staging area in shared memory (32 rows of kOutStageRowBytes).
+//
+// kW13: act = bf16(silu(gate) * up).  Up to 64 output columns at a time go through the staging
+// area and are written back eight lanes per row, so every store instruction covers whole 128-byte
+// lines; the rows of a tile are consecutive rows of act.
+// silu(g) * u in fp32 with the two special-function instructions (exp2, reciprocal) and no
+// division sequence: g / (1 + e^-g) * u to about 2^-22 relative, far inside the bf16 rounding
+// that follows.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return g * r * u;
+}
+
+// 16 gate and 16 up accumulator columns of this lane's row -> 16 bf16 outputs in the staging row.
+__device__ __forceinline__ void swiglu_chunk(const uint32_t (&g)[16], const uint32_t (&u)[16],
+                                             uint8_t* stage_row) {
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    o[i] = pack_bf16(silu_mul(__uint_as_float(g[2 * i]), __uint_as_float(u[2 * i])),
+                     silu_mul(__uint_as_float(g[2 * i + 1]), __uint_as_float(u[2 * i + 1])));
+  uint4* s4 = reinterpret_cast<uint4*>(stage_row);
+  s4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  s4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+__device__ __forceinline__ void drain_w13(const GemmParams& p, uint32_t taddr, uint8_t* stage_out,
+                                          int m_block, int n_tile, int quarter, int lane) {
+#ifdef B200MOE_MEASURE_WITHOUT_EPILOGUE  // measurement builds only: results are not written
+  return;
+#endif
+  __nv_bfloat16* tile_dst = p.out +
+      (static_cast<long long>(m_block) * kBlockM + quarter * 32) * p.out_ld +
+      static_cast<long long>(n_tile) * p.half_n;
+  uint8_t* my_row = stage_out + lane * kOutStageRowBytes;
+  const int chunks = p.half_n >> 4;  // 16 gate columns (and their 16 up columns) per chunk
+  // Two register buffers: the tensor-memory loads of the next chunk are in flight while the
+  // current one goes through the special-function unit.
+  uint32_t ga[16], ua[16], gb[16], ub[16];
+  tmem_ld_32x16(taddr, ga);
+  tmem_ld_32x16(taddr + p.half_n, ua);
+#pragma unroll 1
+  for (int j = 0; j < chunks; j += 2) {
+    tmem_ld_wait();
+    if (j + 1 < chunks) {
+      tmem_ld_32x16(taddr + (j + 1) * 16, gb);
+      tmem_ld_32x16(taddr + p.half_n + (j + 1) * 16, ub);
+    }
+    swiglu_chunk(ga, ua, my_row + (j & 3) * 32);
+    if (j + 1 < chunks) {
+      tmem_ld_wait();
+      if (j + 2 < chunks) {
+        tmem_ld_32x16(taddr + (j + 2) * 16, ga);
+        tmem_ld_32x16(taddr + p.half_n + (j + 2) * 16, ua);
+      }
+      swiglu_chunk(gb, ub, my_row + ((j + 1) & 3) * 32);
+    }
+    if (((j + 2) & 3) == 0 || j + 2 >= chunks) {
+      // Up to 64 staged columns go out, eight lanes per row.
+      const int c0 = (j & ~3) * 16;
+      const int width = min(64, p.half_n - c0);
+      __syncwarp();
+      const int piece = lane & 7;
+      if (piece * 8 < width) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
+          *reinterpret_cast<uint4*>(tile_dst + static_cast<long long>(r) * p.out_ld + c0 + piece * 8) = o;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// kW2: out[pair] = bf16(topk_weights[pair] * acc).  With an output table the row goes straight to
+// the GPU that owns the token (a plain store through a peer mapping): the return all-to-all is
+// this epilogue.  64 columns at a time: every lane scales and packs its own row into the warp's
+// staging area, then the warp writes the 32 rows back out eight lanes per row, so that each store
+// instruction covers four whole 128-byte lines (what a peer mapping or L2 likes) instead of 32
+// scattered 16-byte pieces.  Padding slots are skipped.
+__device__ __forceinline__ void drain_w2(const GemmParams& p, uint32_t taddr, uint8_t* stage_out,
+                                         int m_block, int n_tile, int quarter, int lane) {
+#ifdef B200MOE_MEASURE_WITHOUT_EPILOGUE  // measurement builds only: results are not written
+  return;
+#endif
+  const long long slot = static_cast<long long>(m_block) * kBlockM + quarter * 32 + lane;
+  const int pair = p.sorted[slot];
+  const bool live = pair >= 0 && pair < p.num_pairs;
+  const float w = live ? p.topk_weights[pair] : 0.f;
+  __nv_bfloat16* base = p.out;
+  long long out_row = live ? pair : 0;
+  if (p.out_table != nullptr && live) {
+    const long long owner = out_row / p.pairs_per_rank;
+    base = p.out_table[owner];
+    out_row -= owner * p.pairs_per_rank;
+  }
+  __nv_bfloat16* dst = base + out_row * p.out_ld + static_cast<long long>(n_tile) * kBlockN;
+  const unsigned long long dst_bits = live ? reinterpret_cast<unsigned long long>(dst) : 0ull;
+#pragma unroll 1
+  for (int ch = 0; ch < kBlockN / 64; ++ch) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr + ch * 64 + h * 32, v);
+      tmem_ld_wait();
+      uint4* s4 = reinterpret_cast<uint4*>(stage_out + lane * kOutStageRowBytes + h * 64);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack_bf16(__uint_as_float(v[8 * q + 0]) * w, __uint_as_float(v[8 * q + 1]) * w);
+        o.y = pack_bf16(__uint_as_float(v[8 * q + 2]) * w, __uint_as_float(v[8 * q + 3]) * w);
+        o.z = pack_bf16(__uint_as_float(v[8 * q + 4]) * w, __uint_as_float(v[8 * q + 5]) * w);
+        o.w = pack_bf16(__uint_as_float(v[8 * q + 6]) * w, __uint_as_float(v[8 * q + 7]) * w);
+        s4[q] = o;
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + (lane >> 3), piece = lane & 7;
+      const unsigned long long row_dst = __shfl_sync(0xffffffffu, dst_bits, r);
+      if (row_dst != 0ull) {
+        const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
+        *reinterpret_cast<uint4*>(row_dst + static_cast<unsigned long long>(ch) * 128 + piece * 16) = o;
+      }
+    }
+    __syncwarp();
+  }
+}
+
 template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -455,14 +596,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quarter = warp & 3;               // TMEM lanes this warp may read: 32*quarter ..
-    const int row_in_tile = quarter * 32 + lane;
     bool ok = true;
     long long it = 0;
     for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
       const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off, p.m_group);
       const int acc = static_cast<int>(it & 1);
       const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
-      const long long slot = static_cast<long long>(c.m_block) * kBlockM + row_in_tile;
       // All lanes of the warp must leave together: the wait result is made warp-uniform.
       int good = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, 0x301) ? 1 : 0;
       good = __all_sync(0xffffffffu, good);
@@ -470,102 +609,354 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * kBlockN);
+      uint8_t* stage_out = smem + kStages * kStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
       if (kIsW13) {
-        // Up to 64 output columns at a time through the warp's staging area, written back eight
-        // lanes per row (see the kW2 branch); the rows of a tile are consecutive rows of act.
-        uint8_t* stage_out = smem + kStages * kStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
-        __nv_bfloat16* tile_dst = p.out +
-            (static_cast<long long>(c.m_block) * kBlockM + quarter * 32) * p.out_ld +
-            static_cast<long long>(c.n_tile) * p.half_n;
-#pragma unroll 1
-        for (int c0 = 0; c0 < p.half_n; c0 += 64) {
-          const int width = min(64, p.half_n - c0);  // a multiple of 16
-#pragma unroll 1
-          for (int j = 0; j < width; j += 16) {
-            uint32_t g[16], u[16];
-            tmem_ld_32x16(taddr + c0 + j, g);
-            tmem_ld_32x16(taddr + p.half_n + c0 + j, u);
-            tmem_ld_wait();
-            uint32_t o[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
-              const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
-              const float a0 = g0 / (1.0f + __expf(-g0)) * u0;
-              const float a1 = g1 / (1.0f + __expf(-g1)) * u1;
-              o[i] = pack_bf16(a0, a1);
-            }
-            uint4* s4 = reinterpret_cast<uint4*>(stage_out + lane * kOutStageRowBytes + j * 2);
-            s4[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            s4[1] = make_uint4(o[4], o[5], o[6], o[7]);
-          }
-          __syncwarp();
-          const int piece = lane & 7;
-          if (piece * 8 < width) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = i * 4 + (lane >> 3);
-              const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
-              *reinterpret_cast<uint4*>(tile_dst + static_cast<long long>(r) * p.out_ld + c0 + piece * 8) = o;
-            }
-          }
-          __syncwarp();
-        }
+        drain_w13(p, taddr, stage_out, c.m_block, c.n_tile, quarter, lane);
       } else {
-        const int pair = p.sorted[slot];
-        const bool live = pair >= 0 && pair < p.num_pairs;
-        const float w = live ? p.topk_weights[pair] : 0.f;
-        // With an output table the row goes straight to the GPU that owns the token (a plain
-        // store through a peer mapping): the return all-to-all is this epilogue.
-        __nv_bfloat16* base = p.out;
-        long long out_row = live ? pair : 0;
-        if (p.out_table != nullptr && live) {
-          const long long owner = out_row / p.pairs_per_rank;
-          base = p.out_table[owner];
-          out_row -= owner * p.pairs_per_rank;
-        }
-        __nv_bfloat16* dst = base + out_row * p.out_ld + static_cast<long long>(c.n_tile) * kBlockN;
-        // 64 columns at a time: every lane scales and packs its own row into the warp's staging
-        // area, then the warp writes the 32 rows back out eight lanes per row, so that each store
-        // instruction covers four whole 128-byte lines (what a peer mapping or L2 likes) instead
-        // of 32 scattered 16-byte pieces.
-        uint8_t* stage_out = smem + kStages * kStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
-        const unsigned long long dst_bits = live ? reinterpret_cast<unsigned long long>(dst) : 0ull;
-#pragma unroll 1
-        for (int ch = 0; ch < kBlockN / 64; ++ch) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t v[32];
-            tmem_ld_32x32(taddr + ch * 64 + h * 32, v);
-            tmem_ld_wait();
-            uint4* s4 = reinterpret_cast<uint4*>(stage_out + lane * kOutStageRowBytes + h * 64);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(v[8 * q + 0]) * w, __uint_as_float(v[8 * q + 1]) * w);
-              o.y = pack_bf16(__uint_as_float(v[8 * q + 2]) * w, __uint_as_float(v[8 * q + 3]) * w);
-              o.z = pack_bf16(__uint_as_float(v[8 * q + 4]) * w, __uint_as_float(v[8 * q + 5]) * w);
-              o.w = pack_bf16(__uint_as_float(v[8 * q + 6]) * w, __uint_as_float(v[8 * q + 7]) * w);
-              s4[q] = o;
-            }
-          }
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = i * 4 + (lane >> 3), piece = lane & 7;
-            const unsigned long long row_dst = __shfl_sync(0xffffffffu, dst_bits, r);
-            if (row_dst != 0ull) {
-              const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
-              *reinterpret_cast<uint4*>(row_dst + static_cast<unsigned long long>(ch) * 128 + piece * 16) = o;
-            }
-          }
-          __syncwarp();
-        }
+        drain_w2(p, taddr, stage_out, c.m_block, c.n_tile, quarter, lane);
       }
       // Hand the accumulator back to the MMA warp.
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // Give bulk copies that may still be in flight time to land before shared memory is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < (1ll << 22)) {}
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ================================================================================================
+// Two-block variant of the one-CTA kernel: one CTA computes TWO 128-row M blocks of the same expert
+// against one weight stage.  Per 256 x 256 x 64 multiply-accumulates it stages 32 KiB of
+// activation rows (one TMA box of 256 consecutive rows) and 32 KiB of weights, instead of 2 x 48 KiB
+// for two independent 128 x 256 tiles, while the MMAs stay M = 128 and token alignment stays 128.
+//
+// Both 256-column halves of TMEM are accumulators of the same tile, so tile i + 1 cannot start
+// while tile i is drained from both.  The overlap that is left: the epilogue drains block 0 first
+// and hands its accumulator back; the MMA thread then runs block 0 of the next tile over the first
+// kDualStages K steps (whose stages the producer filled during the drain) before it needs block
+// 1's accumulator, and only then issues block 1's MMAs for those K steps and releases the stages.
+// The last kDualStages K steps mirror that: block 0 finishes them first and is handed to the
+// epilogue (its own "accumulator full" barrier) while block 1 runs them.  What stays exposed per
+// tile is about twice the drain time of one accumulator minus twice kDualStages K steps.
+//
+// Tile sequence.  An expert with an odd number of M blocks ends in a one-block tile.  Tiles are
+// dealt round-robin to the CTAs; a last round that would keep fewer than half of the CTAs busy is
+// dealt as one-block tiles instead, so that round costs half as much.
+// ================================================================================================
+constexpr int kDualStages = 3;
+constexpr int kDualABytes = 2 * kABytes;                      // 32768: 256 rows x 64 columns
+constexpr int kDualStageBytes = kDualABytes + kBBytes;        // 65536
+constexpr int kDualSmemBytes = kDualStages * kDualStageBytes + kOutStageBytes + kSmemAlignSlack;
+// Batch size from which the two-block kernel is chosen, in average M blocks per expert.  Measured
+// on B200 at Mixtral shape, interleaved runs: the second GEMM (K = 14336, epilogue negligible)
+// gains 3-10 % at T = 8192 and 10 % at T = 16384 and loses below about six blocks per expert,
+// where the round-robin deal of tiles that cost one or two units leaves CTAs idle; the first GEMM
+// (K = 4096, so the drain that no longer overlaps the next tile's MMAs weighs more) gains 3-4 % at
+// T = 16384 and nothing at T = 8192.
+constexpr int kDualMinBlocksPerExpertW2 = 6;
+constexpr int kDualMinBlocksPerExpertW13 = 24;
+
+struct DualTile {
+  int expert;
+  int m_block;   // first 128-row block of the tile
+  int n_tile;
+  int m_count;   // 2, 1, or 0 (an empty slot of the split last round)
+};
+
+struct DualSeq {
+  const int* blk_off;    // [E + 1] M-block offsets per expert
+  const int* unit_off;   // [E + 1] offsets in two-block units (ceil(blocks / 2) per expert)
+  int n_tiles, num_experts, unit_group;
+  long long total;       // tiles when every unit is one tile
+  long long cut;         // tiles [cut, total) are dealt as one-block halves
+};
+
+// The i-th tile of this CTA; false when the CTA has no more work.
+__device__ __forceinline__ bool dual_tile_at(const DualSeq& q, long long i, DualTile* t) {
+  const long long grid = gridDim.x;
+  const long long mine = static_cast<long long>(blockIdx.x) < q.cut
+                             ? (q.cut - blockIdx.x + grid - 1) / grid : 0;
+  long long tile;
+  int half = -1;
+  if (i < mine) {
+    tile = blockIdx.x + i * grid;
+  } else {
+    const long long v = blockIdx.x + (i - mine) * grid;
+    if (v >= 2 * (q.total - q.cut)) return false;
+    tile = q.cut + (v >> 1);
+    half = static_cast<int>(v & 1);
+  }
+  const TileCoord c = decode_tile(tile, q.n_tiles, q.num_experts, q.unit_off, q.unit_group);
+  const int unit = c.m_block - q.unit_off[c.expert];
+  const int cnt = q.blk_off[c.expert + 1] - q.blk_off[c.expert];
+  const int natural = 2 * unit + 1 < cnt ? 2 : 1;
+  t->expert = c.expert;
+  t->n_tile = c.n_tile;
+  t->m_block = q.blk_off[c.expert] + 2 * unit + (half > 0 ? 1 : 0);
+  t->m_count = half < 0 ? natural : (half == 0 ? 1 : natural - 1);
+  return true;
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box of 128 rows
+                         const __grid_constant__ CUtensorMap tmap_a2,   // box of 256 rows
+                         const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[kDualStages], empty_bar[kDualStages], tmem_full_bar[2],
+      tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_blk_cnt[kMaxExperts];
+  __shared__ int s_blk_off[kMaxExperts + 1];
+  __shared__ int s_unit_off[kMaxExperts + 1];
+  __shared__ int s_abort;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + kSmemAlignSlack - 1) &
+      ~static_cast<uintptr_t>(kSmemAlignSlack - 1));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ------------------------------------------------------------------ prologue
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_a2);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < kDualStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], kEpilogueWarps);
+    }
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (threadIdx.x < kMaxExperts) s_blk_cnt[threadIdx.x] = 0;
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  __syncthreads();
+  pdl_wait();  // everything above touched only this CTA's shared and tensor memory
+  pdl_launch_dependents();
+  long long npp = *p.npp;
+  if (npp > p.capacity) npp = p.capacity;
+  const int num_blocks = static_cast<int>(npp / kBlockM);
+  for (int b = threadIdx.x; b < num_blocks; b += kThreads) {
+    const int e = p.expert_ids[b];
+    if (e >= 0 && e < p.num_experts) atomicAdd(&s_blk_cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0, units = 0;
+    for (int e = 0; e < p.num_experts; ++e) {
+      s_blk_off[e] = acc;
+      s_unit_off[e] = units;
+      acc += s_blk_cnt[e];
+      units += (s_blk_cnt[e] + 1) >> 1;
+    }
+    s_blk_off[p.num_experts] = acc;
+    s_unit_off[p.num_experts] = units;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_flag = &s_abort;
+
+  DualSeq seq;
+  seq.blk_off = s_blk_off;
+  seq.unit_off = s_unit_off;
+  seq.n_tiles = p.n_tiles;
+  seq.num_experts = p.num_experts;
+  seq.unit_group = p.m_group > 0 ? (p.m_group + 1) / 2 : 0;
+  seq.total = static_cast<long long>(s_unit_off[p.num_experts]) * p.n_tiles;
+  seq.cut = seq.total - seq.total % gridDim.x;
+  if (2 * (seq.total - seq.cut) > static_cast<long long>(gridDim.x)) seq.cut = seq.total;
+
+  constexpr bool kIsW13 = (kMode != kW2);
+  const int b_tx_bytes = p.stage_tx_bytes - kABytes;  // weight bytes of one stage
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      DualTile t;
+      for (long long i = 0; ok && dual_tile_at(seq, i, &t); ++i) {
+        if (t.m_count == 0) continue;
+        const int a_row = t.m_block * kBlockM;
+        const int b_row0 = t.expert * p.b_rows_per_expert +
+                           t.n_tile * (kIsW13 ? p.half_n : kBlockN);
+        const uint32_t tx = b_tx_bytes + t.m_count * kABytes;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x121)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kDualStageBytes;
+          uint8_t* sb = sa + kDualABytes;
+          mbar_expect_tx(&full_bar[stage], tx);
+          tma_load_2d(sa, t.m_count == 2 ? &tmap_a2 : &tmap_a, &full_bar[stage], kb * kBlockK, a_row);
+          if (kIsW13) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
+            tma_load_2d(sb + p.half_n * (kBlockK * 2), &tmap_b, &full_bar[stage], kb * kBlockK,
+                        b_row0 + p.inter);
+          } else {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
+          }
+          if (++stage == kDualStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long it = 0;
+      DualTile t;
+      const uint32_t acc0 = tmem_base, acc1 = tmem_base + kBlockN;
+      for (long long i = 0; ok && dual_tile_at(seq, i, &t); ++i) {
+        if (t.m_count == 0) continue;
+        const uint32_t par = static_cast<uint32_t>(it & 1);
+        ++it;
+        if (!mbar_wait(&tmem_empty_bar[0], par ^ 1, abort_flag, 0x221)) { ok = false; break; }
+        tc_fence_after();
+        int kb = 0;
+        if (t.m_count == 2) {
+          // Block 0 runs ahead over the first K steps while block 1's accumulator is drained.
+          const int head = p.k_blocks < kDualStages ? p.k_blocks : kDualStages;
+          for (int h = 0; ok && h < head; ++h) {
+            const int st = stage + h < kDualStages ? stage + h : stage + h - kDualStages;
+            const uint32_t ph = stage + h < kDualStages ? phase : phase ^ 1;
+            if (!mbar_wait(&full_bar[st], ph, abort_flag, 0x222)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + st * kDualStageBytes);
+            const uint32_t sb = sa + kDualABytes;
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), make_smem_desc(sb + k * kUmmaK * 2),
+                        p.idesc, (h | k) != 0 ? 1u : 0u);
+          }
+          if (!ok) break;
+          if (!mbar_wait(&tmem_empty_bar[1], par ^ 1, abort_flag, 0x223)) { ok = false; break; }
+          tc_fence_after();
+          for (int h = 0; h < head; ++h) {
+            const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
+            const uint32_t sb = sa + kDualABytes;
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              umma_bf16(acc1, make_smem_desc(sa + kABytes + k * kUmmaK * 2),
+                        make_smem_desc(sb + k * kUmmaK * 2), p.idesc, (h | k) != 0 ? 1u : 0u);
+            umma_commit(&empty_bar[stage]);
+            if (++stage == kDualStages) { stage = 0; phase ^= 1; }
+          }
+          // The last K steps mirror the first: block 0 finishes them first and is handed to the
+          // epilogue while block 1 runs them.
+          const int tail = p.k_blocks - head >= kDualStages ? kDualStages : 0;
+          for (kb = head; kb < p.k_blocks - tail; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x224)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
+            const uint32_t sb = sa + kDualABytes;
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              const uint64_t bdesc = make_smem_desc(sb + k * kUmmaK * 2);
+              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), bdesc, p.idesc, 1u);
+              umma_bf16(acc1, make_smem_desc(sa + kABytes + k * kUmmaK * 2), bdesc, p.idesc, 1u);
+            }
+            umma_commit(&empty_bar[stage]);
+            if (++stage == kDualStages) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          for (int h = 0; ok && h < tail; ++h) {
+            const int st = stage + h < kDualStages ? stage + h : stage + h - kDualStages;
+            const uint32_t ph = stage + h < kDualStages ? phase : phase ^ 1;
+            if (!mbar_wait(&full_bar[st], ph, abort_flag, 0x227)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + st * kDualStageBytes);
+            const uint32_t sb = sa + kDualABytes;
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), make_smem_desc(sb + k * kUmmaK * 2),
+                        p.idesc, 1u);
+          }
+          if (!ok) break;
+          umma_commit(&tmem_full_bar[0]);  // block 0 complete
+          for (int h = 0; h < tail; ++h) {
+            const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
+            const uint32_t sb = sa + kDualABytes;
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              umma_bf16(acc1, make_smem_desc(sa + kABytes + k * kUmmaK * 2),
+                        make_smem_desc(sb + k * kUmmaK * 2), p.idesc, 1u);
+            umma_commit(&empty_bar[stage]);
+            if (++stage == kDualStages) { stage = 0; phase ^= 1; }
+          }
+          umma_commit(&tmem_full_bar[1]);  // block 1 complete
+        } else {
+          if (!mbar_wait(&tmem_empty_bar[1], par ^ 1, abort_flag, 0x225)) { ok = false; break; }
+          tc_fence_after();
+          for (kb = 0; kb < p.k_blocks; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x226)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
+            const uint32_t sb = sa + kDualABytes;
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), make_smem_desc(sb + k * kUmmaK * 2),
+                        p.idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit(&empty_bar[stage]);
+            if (++stage == kDualStages) { stage = 0; phase ^= 1; }
+          }
+          if (ok) {
+            umma_commit(&tmem_full_bar[0]);
+            umma_commit(&tmem_full_bar[1]);  // keeps the two barriers in step; nothing to drain
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;               // TMEM lanes this warp may read: 32*quarter ..
+    uint8_t* stage_out = smem + kDualStages * kDualStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    bool ok = true;
+    long long it = 0;
+    DualTile t;
+    for (long long i = 0; ok && dual_tile_at(seq, i, &t); ++i) {
+      if (t.m_count == 0) continue;
+      const uint32_t par = static_cast<uint32_t>(it & 1);
+      ++it;
+      for (int b = 0; b < 2; ++b) {
+        // All lanes of the warp must leave together: the wait result is made warp-uniform.
+        int good = mbar_wait(&tmem_full_bar[b], par, abort_flag, 0x321 + b) ? 1 : 0;
+        good = __all_sync(0xffffffffu, good);
+        if (!good) { ok = false; break; }
+        tc_fence_after();
+        if (b < t.m_count) {
+          if (kIsW13) {
+            drain_w13(p, taddr + b * kBlockN, stage_out, t.m_block + b, t.n_tile, quarter, lane);
+          } else {
+            drain_w2(p, taddr + b * kBlockN, stage_out, t.m_block + b, t.n_tile, quarter, lane);
+          }
+        }
+        // Hand this accumulator back to the MMA warp.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[b]);
+      }
     }
   }
 
@@ -827,9 +1218,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < 16; ++j) {
             const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
             const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
-            const float a0 = g0 / (1.0f + __expf(-g0)) * u0;
-            const float a1 = g1 / (1.0f + __expf(-g1)) * u1;
-            o[j] = pack_bf16(a0, a1);
+            o[j] = pack_bf16(silu_mul(g0, u0), silu_mul(g1, u1));
           }
           uint4* d4 = reinterpret_cast<uint4*>(dst + ch * 32);
 #pragma unroll
@@ -939,6 +1328,34 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cu
 }
 
 template <int kMode>
+int launch_dual(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb,
+                const GemmParams& p, cudaStream_t st) {
+  const cudaError_t attr_err = cudaFuncSetAttribute(
+      grouped_gemm_dual_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDualSmemBytes);
+  if (attr_err != cudaSuccess)
+    return fail(B200MOE_ERR_CUDA, "grouped_gemm: cannot reserve %d bytes of shared memory: %s",
+                kDualSmemBytes, cudaGetErrorString(attr_err));
+  launch_pdl(grouped_gemm_dual_kernel<kMode>, dim3(sm_count()), dim3(kThreads), kDualSmemBytes, st,
+             ta, ta2, tb, p);
+  return check_launch("grouped_gemm (two-block tiles)");
+}
+
+// Tiling of the one-CTA kernels: 0 = chosen by batch size, 1 = one M block per tile, 2 = two.
+std::atomic<int> g_tiling{0};
+
+// Two-block tiles pay off once most experts hold several M blocks: the weight stage is then
+// shared by two blocks almost everywhere.  With one block per expert (decode-sized batches) every
+// tile would be a one-block tile without the double-buffered accumulator, so the one-block kernel
+// is kept there.  `capacity` = pairs + num_experts * 127 bounds the padded row count.
+bool use_two_block_tiles(int64_t capacity, int num_experts, int min_blocks_per_expert) {
+  const int mode = g_tiling.load(std::memory_order_relaxed);
+  if (capacity < 2 * kBlockM) return false;
+  if (mode != 0) return mode == 2;
+  const int64_t pairs = capacity - static_cast<int64_t>(num_experts) * (kBlockM - 1);
+  return pairs >= static_cast<int64_t>(num_experts) * kBlockM * min_blocks_per_expert;
+}
+
+template <int kMode>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
   const cudaError_t attr_err = cudaFuncSetAttribute(
       grouped_gemm_pair_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
@@ -1027,11 +1444,15 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(a_sorted, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  // The two-CTA kernel has a fixed 128 + 128 column tile; the one-CTA kernel picks its width.
+  // The two-CTA kernel has a fixed 128 + 128 column tile; the one-CTA kernels pick their width.
+  const bool two_block = block_m == kBlockM &&
+                         use_two_block_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW13);
   const int half_n = block_m == kPairBlockM ? kBlockN / 2
                                             : choose_half_n(sorted_capacity, num_experts, inter);
-  CUtensorMap ta, tb;
+  CUtensorMap ta, ta2, tb;
   if (int rc = make_tmap(&ta, a_sorted, sorted_capacity, hidden, kBlockM, name)) return rc;
+  if (two_block)
+    if (int rc = make_tmap(&ta2, a_sorted, sorted_capacity, hidden, 2 * kBlockM, name)) return rc;
   if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden, half_n,
                          name))
     return rc;
@@ -1050,6 +1471,7 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   set_width(&p, 2 * half_n);
   p.m_group = m_group_for(hidden * 2);
   if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  if (two_block) return launch_dual<kW13>(ta, ta2, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
 }
 
@@ -1124,8 +1546,12 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16) || !aligned_to(out, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  CUtensorMap ta, tb;
+  const bool two_block = block_m == kBlockM &&
+                         use_two_block_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2);
+  CUtensorMap ta, ta2, tb;
   if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
+  if (two_block)
+    if (int rc = make_tmap(&ta2, act, sorted_capacity, inter, 2 * kBlockM, name)) return rc;
   // The two-CTA kernel fetches the B tile as two boxes of 128 rows, one per CTA.
   if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter,
                          block_m == kPairBlockM ? kBlockN / 2 : kBlockN, name))
@@ -1147,6 +1573,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  if (two_block) return launch_dual<kW2>(ta, ta2, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
 }
 
@@ -1172,8 +1599,12 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  CUtensorMap ta, tb;
+  const bool two_block = block_m == kBlockM &&
+                         use_two_block_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2);
+  CUtensorMap ta, ta2, tb;
   if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
+  if (two_block)
+    if (int rc = make_tmap(&ta2, act, sorted_capacity, inter, 2 * kBlockM, name)) return rc;
   if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter,
                          block_m == kPairBlockM ? kBlockN / 2 : kBlockN, name))
     return rc;
@@ -1196,7 +1627,16 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  if (two_block) return launch_dual<kW2>(ta, ta2, tb, p, static_cast<cudaStream_t>(stream));
   return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_gemm_set_tiling(int mode) {
+  using namespace b200moe;
+  if (mode < 0 || mode > 2)
+    return fail(B200MOE_ERR_SHAPE, "gemm_set_tiling: mode must be 0 (automatic), 1 or 2, got %d", mode);
+  g_tiling.store(mode, std::memory_order_relaxed);
+  return B200MOE_OK;
 }
 
 extern "C" int b200moe_gemm_device_status(int reset) {

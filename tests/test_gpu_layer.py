@@ -24,17 +24,30 @@ def gemm_status():
     return _lib.load().b200moe_gemm_device_status(1)
 
 
+@pytest.fixture(autouse=True)
+def _automatic_tiling():
+    """Tests that force a tiling of the grouped GEMMs leave the process-wide setting at automatic."""
+    yield
+    _lib.load().b200moe_gemm_set_tiling(0)
+
+
+# (block_m, tiling): one 128-row block per tile, two blocks per tile, CTA pairs on 256-row tiles.
+TILINGS = [(128, 1), (128, 2), (256, 0)]
+
+
 def aligned(ids_flat, E, block_m=BLOCK_SIZE_M):
     s, e, n, _ = moe_oracle.align_ref(ids_flat, block_m, E)
     return s, e, n
 
 
 # ------------------------------------------------------------------------------- grouped GEMMs
-@pytest.mark.parametrize("block_m", [128, 256])
+@pytest.mark.parametrize("block_m,tiling", TILINGS)
 @pytest.mark.parametrize("T,H,I,E", [(100, 256, 128, 8), (300, 512, 1024, 8), (37, 64, 256, 3),
-                                     (1000, 1024, 512, 8), (1, 256, 128, 8), (3000, 512, 256, 8)])
-def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m):
+                                     (1000, 1024, 512, 8), (1, 256, 128, 8), (3000, 512, 256, 8),
+                                     (2500, 128, 128, 2)])
+def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m, tiling):
     lib = _lib.load()
+    _lib.check(lib.b200moe_gemm_set_tiling(tiling), "set_tiling")
     g = torch.Generator().manual_seed(T + H)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)
     w13 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).to(torch.bfloat16)
@@ -65,11 +78,12 @@ def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m):
     assert (got[used:] == 9.0).all(), "rows beyond num_tokens_post_pad were written"
 
 
-@pytest.mark.parametrize("block_m", [128, 256])
+@pytest.mark.parametrize("block_m,tiling", TILINGS)
 @pytest.mark.parametrize("T,H,I,E", [(100, 256, 128, 8), (300, 512, 1024, 8), (37, 256, 64, 3),
-                                     (1000, 1024, 512, 8), (3000, 512, 256, 8)])
-def test_grouped_gemm_w2_scale(T, H, I, E, block_m):
+                                     (1000, 1024, 512, 8), (3000, 512, 256, 8), (2500, 256, 128, 2)])
+def test_grouped_gemm_w2_scale(T, H, I, E, block_m, tiling):
     lib = _lib.load()
+    _lib.check(lib.b200moe_gemm_set_tiling(tiling), "set_tiling")
     g = torch.Generator().manual_seed(T + I)
     ids = torch.randint(0, E, (T * 2,), generator=g, dtype=torch.int32)
     s, e, n = aligned(ids.numpy(), E, block_m)
@@ -305,20 +319,24 @@ def test_layer_token_counts(T):
     check_layer(make_inputs(wl), wl)
 
 
-@pytest.mark.parametrize("T", [5, 700, 4096])
+@pytest.mark.parametrize("T", [5, 700, 4096, 20000])
 def test_layer_block_sizes_agree_bit_for_bit(T):
-    """The one-CTA (128-row) and two-CTA (256-row) tilings run the same arithmetic per row."""
+    """One block per tile, two blocks per tile and the two-CTA (256-row) tiling run the same
+    arithmetic per row.  T=20000 gives every expert many M blocks, an odd count for some, and a
+    last round of tiles short enough to be dealt as one-block halves."""
     from electrock_infer_b200.layers.moe import fused_moe as fm
     wl = MoEWorkload("t", T, 512, 512, seed=100 + T, logit_bias=(1, 0, 0, 0, 0, 0, -1, -3))
     inp = make_inputs(wl)
     outs = []
     try:
-        for bm in (128, 256):
+        for bm, tiling in TILINGS:
             fm.FORCE_BLOCK_M = bm
+            _lib.check(_lib.load().b200moe_gemm_set_tiling(tiling), "set_tiling")
             outs.append(run_layer(inp, wl)[1].clone())
     finally:
         fm.FORCE_BLOCK_M = None
     assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[2])
     assert fm.choose_block_m(8192, 2, 8) == 128
     check_layer(inp, wl)
 
