@@ -3,6 +3,7 @@
 Usage (only where the reference tree is available; the fixtures themselves are committed):
 
     python tests/golden/make_golden.py /path/to/electrock-infer
+    ELECTROCK_REFERENCE=/path/to/electrock-infer python tests/golden/make_golden.py
 
 What is run, unmodified, from the reference tree:
   * ``topk_softmax_torch`` and ``fused_topk``      layers/moe/softmax_topk.py, layers/moe/fused_moe.py
@@ -12,7 +13,8 @@ What is run, unmodified, from the reference tree:
   * ``cpu_attention_golden``                       test/example/test_paged_attn.py:24-52
   * ``store_kvcache_naive_torch`` and the Triton ``store_kvcache_triton`` (interpreted)
                                                    test/example/test_store_kvcache.py:6-72
-``--only kv`` regenerates just the KV-cache fixture.
+  * ``RMSNorm`` (with and without residual)       layers/layernorm.py:5-57
+``--only kv`` / ``--only rmsnorm`` regenerate just that fixture.
 The reference's compiled module ``electrock_infer._C`` cannot be built here (it targets another
 vendor's compiler), so a stand-in module provides the three ops ``fused_experts`` calls, written
 from the reference's documented formulas (the same functions the oracle exposes).
@@ -122,6 +124,42 @@ def make_kv() -> None:
     np.savez_compressed(HERE / "kv.npz", **kv)
 
 
+def make_rmsnorm() -> None:
+    """Outputs of the reference's ``RMSNorm.forward`` (layers/layernorm.py:45-57), with and without
+    a residual, on seeded inputs; the oracle restatement must reproduce them bit for bit."""
+    from electrock_infer.layers.layernorm import RMSNorm
+    sys.path.insert(0, str(REPO / "tests"))
+    from rmsnorm_cases import RMSNORM_CASES, rmsnorm_inputs
+    out = {}
+    for name, (rows, hidden, dtype, eps) in RMSNORM_CASES.items():
+        x, residual, weight, eps = rmsnorm_inputs(name)
+        norm = RMSNorm(hidden, eps=eps).to(dtype)
+        with torch.no_grad():
+            norm.weight.copy_(weight)
+            y = norm(x.clone())
+            y_res, new_res = norm(x.clone(), residual.clone())
+        mine = moe_oracle.rms_norm_ref(x, weight, eps)
+        mine_res, mine_new = moe_oracle.rms_norm_ref(x, weight, eps, residual)
+        assert torch.equal(y, mine) and torch.equal(y_res, mine_res), \
+            f"{name}: oracle restatement differs from the reference RMSNorm"
+        if dtype == torch.float32:
+            # In fp32 the reference's casts are no-ops, so its in-place scaling also rewrites the
+            # tensor it returns as the new residual (layers/layernorm.py:36-41): the residual it
+            # hands back IS the normalised output.  The 16-bit dtypes (what the model runs in)
+            # return the sum.  The fixture records what the reference returns; the oracle and the
+            # kernels return the sum for every dtype.
+            assert torch.equal(new_res, y_res)
+            assert torch.equal(mine_new, x + residual)
+        else:
+            assert torch.equal(new_res, mine_new), f"{name}: residual differs from the reference"
+        as_bits = (lambda t: t.view(torch.int16).numpy()) if dtype != torch.float32 else (lambda t: t.numpy())
+        out[f"{name}_digest"] = np.array(digest(x, residual, weight))
+        out[f"{name}_y"] = as_bits(y)
+        out[f"{name}_y_with_residual"] = as_bits(y_res)
+        out[f"{name}_new_residual"] = as_bits(new_res)
+    np.savez_compressed(HERE / "rmsnorm.npz", **out)
+
+
 def run_hf_block(hf, inputs, wl: MoEWorkload, dtype=torch.float32):
     cfg = {"hidden_size": wl.hidden, "intermediate_size": wl.inter, "num_experts": wl.num_experts,
            "top_k": wl.top_k, "hidden_act": "silu"}
@@ -139,12 +177,17 @@ def run_hf_block(hf, inputs, wl: MoEWorkload, dtype=torch.float32):
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--")
-                    else "/root/reference")
+    where = (sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--")
+             else os.environ.get("ELECTROCK_REFERENCE"))
+    if not where or not (Path(where) / "electrock_infer").is_dir():
+        raise SystemExit("give the path of the electrock-infer source tree as the first argument "
+                         "or in ELECTROCK_REFERENCE")
+    ref_root = Path(where)
     fused_moe, topk_softmax_torch, hf, al = load_reference(ref_root)
-    if "--only" in sys.argv and sys.argv[sys.argv.index("--only") + 1] == "kv":
-        make_kv()
-        print("kv.npz", (HERE / "kv.npz").stat().st_size, "bytes")
+    if "--only" in sys.argv:
+        which = sys.argv[sys.argv.index("--only") + 1]
+        {"kv": make_kv, "rmsnorm": make_rmsnorm}[which]()
+        print(f"{which}.npz", (HERE / f"{which}.npz").stat().st_size, "bytes")
         return
 
     # ------------------------------------------------------------------ router
@@ -224,6 +267,7 @@ def main() -> None:
     ops["moe_sum_out_f16"] = torch.sum(ms, dim=1).numpy()
     np.savez_compressed(HERE / "ops.npz", **ops)
     make_kv()
+    make_rmsnorm()
 
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")

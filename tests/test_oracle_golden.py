@@ -172,3 +172,29 @@ def test_paged_store_oracle_matches_reference_torch_and_triton_store(golden):
     k2, v2 = moe_oracle.paged_store_kvcache_ref(c["key"], c["value"], c["k_cache"], c["v_cache"], slots)
     untouched = (k2 == 3.0).all(dim=-1).all(dim=-1).sum().item()
     assert untouched == c["k_cache"].shape[0] * c["k_cache"].shape[1] - int((slots >= 0).sum())
+
+
+def _bits(t):
+    return t.numpy() if t.dtype == torch.float32 else t.view(torch.int16).numpy()
+
+
+@pytest.mark.parametrize("case", ["bf16_h4096", "bf16_h520", "f16_h1024", "f32_h768"])
+def test_rms_norm_oracle_matches_reference_module(golden, case):
+    """The fixture holds what the reference's ``RMSNorm.forward`` (layers/layernorm.py:45-57)
+    returned, with and without a residual; the restatement must give the same bits."""
+    from rmsnorm_cases import rmsnorm_inputs
+    x, residual, weight, eps = rmsnorm_inputs(case)
+    fx = golden["rmsnorm"]
+    assert str(fx[f"{case}_digest"]) == _digest(x, residual, weight)
+    y = moe_oracle.rms_norm_ref(x, weight, eps)
+    y_res, new_res = moe_oracle.rms_norm_ref(x, weight, eps, residual)
+    assert np.array_equal(_bits(y), fx[f"{case}_y"])
+    assert np.array_equal(_bits(y_res), fx[f"{case}_y_with_residual"])
+    if x.dtype == torch.float32:
+        # fp32 only: the reference's no-op casts make its in-place scaling overwrite the tensor it
+        # returns as the residual, which therefore equals its output.  The oracle (and the
+        # kernels) return the sum for every dtype, as the 16-bit paths of the reference do.
+        assert np.array_equal(fx[f"{case}_new_residual"], fx[f"{case}_y_with_residual"])
+        assert torch.equal(new_res, x + residual)
+    else:
+        assert np.array_equal(_bits(new_res), fx[f"{case}_new_residual"])
