@@ -51,44 +51,110 @@ def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: i
     return topk_weights, topk_ids
 
 
+def capacity_bucket(num_tokens: int) -> int:
+    """Token capacity scratch is sized for: the next power of two, at least 256.  A serving loop
+    whose batch size changes every step therefore reallocates only when a batch exceeds every
+    earlier one by a factor, and never in steady state."""
+    return max(256, 1 << max(num_tokens - 1, 0).bit_length())
+
+
 class _Workspace:
-    """Scratch tensors of one ``fused_experts`` call, kept per (device, stream, shape) so that
-    steady-state calls allocate nothing and calls on different streams never share scratch.  The
-    reference allocates its three caches on every call (fused_moe.py:223-239)."""
+    """Scratch tensors of ``fused_experts``, kept per (device, stream, layer shape) and sized for a
+    token capacity bucket; a call uses a prefix of them, so steady-state calls allocate nothing
+    whatever their batch size, and calls on different streams never share scratch.  The reference
+    allocates its three caches on every call (fused_moe.py:223-239).
+
+    CUDA graphs: a captured call keeps raw pointers into these tensors.  An entry used during
+    stream capture is therefore never freed (when a larger batch replaces it, it is retired, not
+    released), and a call that would have to allocate during capture raises instead: run the
+    layer once on the capture stream with the largest batch, or call ``reserve_workspace``,
+    before capturing."""
+
+    MAX_ENTRIES = 8
+    MAX_VIEWS = 32
 
     def __init__(self) -> None:
         self._cache: Dict[tuple, dict] = {}
+        self._retired: list = []
+
+    def _allocate(self, device, max_tokens, topk, num_experts, hidden, inter, block_m) -> dict:
+        pairs = max_tokens * topk
+        capacity = pairs + num_experts * (block_m - 1)
+        blocks = (capacity + block_m - 1) // block_m
+        i32 = dict(dtype=torch.int32, device=device)
+        bf16 = dict(dtype=torch.bfloat16, device=device)
+        return {
+            "max_tokens": max_tokens, "pinned": False, "views": {},
+            "topk_weights": torch.empty(max_tokens, topk, dtype=torch.float32, device=device),
+            "topk_ids": torch.empty(max_tokens, topk, **i32),
+            "sorted_ids": torch.empty(capacity, **i32),
+            "expert_ids": torch.zeros(blocks, **i32),
+            "num_post_pad": torch.zeros(1, **i32),
+            "align_ws": torch.empty(max(_C.align_workspace_numel(pairs, num_experts), 1), **i32),
+            "a_sorted": torch.empty(capacity, hidden, **bf16),
+            "act": torch.empty(capacity, inter, **bf16),
+            "cache3": torch.empty(max_tokens, topk, hidden, **bf16),
+        }
 
     def get(self, device: torch.device, num_tokens: int, topk: int, num_experts: int,
-            hidden: int, inter: int, block_m: int) -> dict:
+            hidden: int, inter: int, block_m: int, reserve_only: bool = False) -> Optional[dict]:
         stream = torch.cuda.current_stream(device).cuda_stream
-        key = (device, stream, num_tokens, topk, num_experts, hidden, inter, block_m)
-        ws = self._cache.get(key)
+        key = (device, stream, topk, num_experts, hidden, inter, block_m)
+        entry = self._cache.get(key)
+        capturing = torch.cuda.is_current_stream_capturing()
+        if entry is None or entry["max_tokens"] < num_tokens:
+            if capturing:
+                raise RuntimeError(
+                    "fused_experts: scratch for this batch size does not exist yet and cannot be "
+                    "allocated during stream capture; run the layer once on this stream with a "
+                    "batch at least this large (or call reserve_workspace) before capturing")
+            if entry is not None and entry["pinned"]:
+                self._retired.append(entry)  # a captured graph may still point into it
+            if entry is None and len(self._cache) >= self.MAX_ENTRIES:
+                for old_key, old in list(self._cache.items()):  # oldest entry no graph refers to
+                    if not old["pinned"]:
+                        del self._cache[old_key]
+                        break
+            entry = self._allocate(device, capacity_bucket(num_tokens), topk, num_experts, hidden,
+                                   inter, block_m)
+            self._cache[key] = entry
+        if capturing:
+            entry["pinned"] = True
+        if reserve_only:
+            return None
+        ws = entry["views"].get(num_tokens)
         if ws is None:
-            if len(self._cache) >= 8:  # bounded: drop the oldest entry
-                self._cache.pop(next(iter(self._cache)))
-            pairs = num_tokens * topk
-            capacity = pairs + num_experts * (block_m - 1)
+            if len(entry["views"]) >= self.MAX_VIEWS:
+                entry["views"].pop(next(iter(entry["views"])))
+            capacity = num_tokens * topk + num_experts * (block_m - 1)
             blocks = (capacity + block_m - 1) // block_m
-            i32 = dict(dtype=torch.int32, device=device)
-            bf16 = dict(dtype=torch.bfloat16, device=device)
             ws = {
                 "capacity": capacity,
-                "topk_weights": torch.empty(num_tokens, topk, dtype=torch.float32, device=device),
-                "topk_ids": torch.empty(num_tokens, topk, **i32),
-                "sorted_ids": torch.empty(capacity, **i32),
-                "expert_ids": torch.zeros(blocks, **i32),
-                "num_post_pad": torch.zeros(1, **i32),
-                "align_ws": torch.empty(max(_C.align_workspace_numel(pairs, num_experts), 1), **i32),
-                "a_sorted": torch.empty(capacity, hidden, **bf16),
-                "act": torch.empty(capacity, inter, **bf16),
-                "cache3": torch.empty(num_tokens, topk, hidden, **bf16),
+                "topk_weights": entry["topk_weights"][:num_tokens],
+                "topk_ids": entry["topk_ids"][:num_tokens],
+                "sorted_ids": entry["sorted_ids"][:capacity],
+                "expert_ids": entry["expert_ids"][:blocks],
+                "num_post_pad": entry["num_post_pad"],
+                "align_ws": entry["align_ws"],
+                "a_sorted": entry["a_sorted"][:capacity],
+                "act": entry["act"][:capacity],
+                "cache3": entry["cache3"][:num_tokens],
             }
-            self._cache[key] = ws
+            entry["views"][num_tokens] = ws
         return ws
 
 
 _workspace = _Workspace()
+
+
+def reserve_workspace(device, max_tokens: int, topk: int, num_experts: int, hidden: int,
+                      inter: int) -> None:
+    """Allocates the scratch of ``fused_experts`` on ``device``'s current stream for batches of up
+    to ``max_tokens`` tokens, so that no later call (smaller or equal) allocates: for serving
+    loops with a known maximum batch and before CUDA graph capture."""
+    device = torch.device(device)
+    _workspace.get(device, max_tokens, topk, num_experts, hidden, inter,
+                   choose_block_m(max_tokens, topk, num_experts), reserve_only=True)
 
 # Optional per-kernel timing for benchmarks: when enabled, every launch of fused_experts is
 # bracketed by a pair of CUDA events on the launching stream.

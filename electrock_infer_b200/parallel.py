@@ -43,7 +43,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import _C, _lib
-from .layers.moe.fused_moe import BLOCK_SIZE_M, _timed
+from .layers.moe.fused_moe import BLOCK_SIZE_M, _timed, capacity_bucket
 
 
 class _RawDeviceMemory:
@@ -148,49 +148,81 @@ class TensorParallelReduce:
     Rounding follows the reference (each rank's two-row sum is rounded to bf16 before the ranks
     are added, layers/moe/mixtral_moe.py:114-116): with two ranks the result has the same bits as
     the NCCL all-reduce; with more it is one fp32 sum in rank order, where an all-reduce rounds
-    between its steps in an order of its own choosing.  Every rank receives the same bits.  ``state`` allocates and synchronises the first time a token
-    count is seen.
+    between its steps in an order of its own choosing.  Every rank receives the same bits.
+    The peer buffers are sized for a token capacity (``capacity_for``) and reused for every
+    smaller batch; ``state`` allocates and synchronises only when a batch exceeds it.
     """
 
     def __init__(self, group=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self._states = {}
+        self._buffers = {}   # (top_k, hidden, device) -> peer buffers sized for a token capacity
 
     def usable(self, num_tokens: int) -> bool:
         return num_tokens > 0 and num_tokens % self.world == 0 and self.world <= 8
 
-    def state(self, num_tokens: int, top_k: int, hidden: int, device: torch.device) -> dict:
-        key = (num_tokens, top_k, hidden, device)
-        st = self._states.get(key)
-        if st is None:
-            per = num_tokens // self.world
-            slot_bytes = per * top_k * hidden * 2
-            recv = PeerBuffer(self.world * slot_bytes, device, self.group)
+    def capacity_for(self, num_tokens: int) -> int:
+        """Token capacity the peer buffers are sized for: the power-of-two bucket of the batch,
+        rounded up to a multiple of the group size.  Every rank sees the same batch size, so
+        every rank computes the same capacity and grows its buffers in the same call."""
+        cap = capacity_bucket(num_tokens)
+        return (cap + self.world - 1) // self.world * self.world
+
+    def reserve(self, max_tokens: int, top_k: int, hidden: int, device: torch.device) -> None:
+        """Collective set-up for batches of up to ``max_tokens`` tokens: no later call within the
+        bound allocates or synchronises."""
+        self._buffers_for(max_tokens, top_k, hidden, device)
+
+    def _buffers_for(self, num_tokens: int, top_k: int, hidden: int, device: torch.device) -> dict:
+        key = (top_k, hidden, device)
+        buf = self._buffers.get(key)
+        if buf is None or buf["cap_tokens"] < num_tokens:
+            if buf is not None:  # a larger batch than ever before: replace the buffers (collective)
+                buf["recv"].close()
+                buf["out"].close()
+                del self._buffers[key]
+            cap = self.capacity_for(num_tokens)
+            recv = PeerBuffer(cap * top_k * hidden * 2, device, self.group)
             try:
-                out = PeerBuffer(num_tokens * hidden * 2, device, self.group)
+                out = PeerBuffer(cap * hidden * 2, device, self.group)
             except PeerMemoryUnavailable:
                 recv.close()
                 raise
+            buf = {"cap_tokens": cap, "recv": recv, "out": out, "per_batch": {},
+                   "token": torch.zeros(1, dtype=torch.int32, device=device)}
+            self._buffers[key] = buf
+        return buf
+
+    def state(self, num_tokens: int, top_k: int, hidden: int, device: torch.device) -> dict:
+        """Buffers and tables for a batch of ``num_tokens`` tokens.  Allocates, maps and
+        synchronises (collectively) only when the batch exceeds the capacity reserved so far; a
+        smaller batch uses a prefix of the same buffers."""
+        buf = self._buffers_for(num_tokens, top_k, hidden, device)
+        st = buf["per_batch"].get(num_tokens)
+        if st is None:
+            if len(buf["per_batch"]) >= 64:
+                buf["per_batch"].pop(next(iter(buf["per_batch"])))
+            per = num_tokens // self.world
+            slot_bytes = per * top_k * hidden * 2
             st = {
-                "recv": recv, "out": out, "tokens_per_rank": per,
+                "recv": buf["recv"], "out": buf["out"], "tokens_per_rank": per, "token": buf["token"],
                 # Where this rank's rows go in every rank's receive buffer.
-                "push_table": torch.tensor([p + self.rank * slot_bytes for p in recv.ptrs],
+                "push_table": torch.tensor([p + self.rank * slot_bytes for p in buf["recv"].ptrs],
                                            dtype=torch.int64, device=device),
-                "out_local": out.local.view(torch.bfloat16).view(num_tokens, hidden),
-                "token": torch.zeros(1, dtype=torch.int32, device=device),
+                "out_local": buf["out"].local.view(torch.bfloat16)[: num_tokens * hidden].view(
+                    num_tokens, hidden),
             }
-            self._states[key] = st
+            buf["per_batch"][num_tokens] = st
         return st
 
     def close(self) -> None:
         """Unmaps and frees the peer-visible buffers (every rank, after the last step has
         finished on every rank)."""
-        for st in self._states.values():
-            st["recv"].close()
-            st["out"].close()
-        self._states.clear()
+        for buf in self._buffers.values():
+            buf["recv"].close()
+            buf["out"].close()
+        self._buffers.clear()
 
     def finish(self, st: dict, output: torch.Tensor, top_k: int) -> None:
         """Everything after the second GEMM: barrier, combine + push, barrier, copy."""
@@ -326,11 +358,15 @@ class ExpertParallelMoE(nn.Module):
     ``forward(hidden_states [T_local, H], router_logits [T_local, E])`` overwrites and returns
     ``hidden_states``.
 
-    The peer-memory exchange is used when every rank holds the same number of tokens, or, with
-    ``max_tokens_per_rank`` set, for ANY token counts up to that bound (ragged batches, ranks with
-    no tokens at all): buffers are sized for the bound once, shorter batches are padded with pair
-    indices the alignment skips, and no step synchronises with the host.  Every rank must then
-    stay within the bound.
+    ``exchange``: with ``max_tokens_per_rank`` set, ``"auto"`` and ``"peer"`` use the peer-memory
+    exchange for ANY token counts up to that bound (ragged batches, ranks with no tokens at all):
+    buffers are sized for the bound once, shorter batches are padded with pair indices the
+    alignment skips, and no step synchronises with the host; every rank must stay within the
+    bound.  Without a bound, ``"auto"`` uses the NCCL all-to-alls (any token counts), and
+    ``"peer"`` is a promise by the caller that every rank passes the same number of tokens in
+    every call (buffers then grow with the largest batch seen).  The constructor arguments must be
+    the same on every rank: they alone decide which collectives a call enters
+    (``peer_capacity``).
     """
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
@@ -392,62 +428,81 @@ class ExpertParallelMoE(nn.Module):
         return recv
 
     # ------------------------------------------------------------------ peer-memory exchange
+    def peer_capacity(self, num_tokens: int) -> Optional[int]:
+        """Tokens per rank the peer-memory buffers must hold for this call, or None when the call
+        takes the NCCL exchange.  The answer must be the same on every rank in every call, or the
+        ranks would enter different collectives; so it depends only on the constructor arguments
+        and, in forced ``"peer"`` mode without a bound, on a token count that the caller
+        guarantees to be equal on all ranks:
+
+        * ``max_tokens_per_rank`` given: always that bound (ragged batches are padded up to it);
+        * ``exchange="peer"`` without a bound: the power-of-two bucket of ``num_tokens``;
+        * ``exchange="auto"`` without a bound, or ``"nccl"``: None.  Token counts that differ
+          between ranks, or change unevenly from call to call, are exactly what the NCCL exchange
+          is for, and nothing that one rank alone can see tells it what the others hold.
+        """
+        if self.exchange == "nccl":
+            return None
+        if self.max_tokens_per_rank is not None:
+            return self.max_tokens_per_rank
+        if self.exchange == "peer":
+            return capacity_bucket(num_tokens)
+        return None
+
     def _peer_state(self, num_tokens: int, hidden: int, device: torch.device):
-        """Buffers of the peer-memory path, or None when it does not apply (set-up: allocates and
-        synchronises the first time).  With ``max_tokens_per_rank`` the buffers hold that many
-        tokens per rank; otherwise every rank must hold exactly ``num_tokens`` tokens."""
-        bounded = self.max_tokens_per_rank is not None
-        cap_tokens = self.max_tokens_per_rank if bounded else num_tokens
-        key = (cap_tokens, bounded, hidden, device)
-        if key in self._peer_states:
-            return self._peer_states[key]
-        usable = cap_tokens > 0
-        if not bounded:
-            counts = [None] * self.ep_size
-            dist.all_gather_object(counts, num_tokens, group=self.group)
-            usable = usable and all(c == num_tokens for c in counts)
-        state = None
-        if usable:
-            ep, k, per = self.ep_size, self.top_k, self.experts_per_rank
-            pairs_total = ep * cap_tokens * k
-            cap = pairs_total + per * (BLOCK_SIZE_M - 1)
-            i32 = dict(dtype=torch.int32, device=device)
-            bf16 = dict(dtype=torch.bfloat16, device=device)
+        """Buffers of the peer-memory path, or None when the call takes the NCCL exchange.
+        Set-up (allocation, mapping, synchronisation) happens the first time and whenever the
+        capacity grows, on every rank in the same call."""
+        cap_tokens = self.peer_capacity(num_tokens)
+        if cap_tokens is None:
+            return None
+        key = (hidden, device)
+        state = self._peer_states.get(key)
+        if state is not None and state["cap_tokens"] >= cap_tokens:
+            return state
+        if state is not None:  # the bucket grew: replace the buffers (collective)
+            state["x_stage"].close()
+            state["cache3"].close()
+            del self._peer_states[key]
+        ep, k, per = self.ep_size, self.top_k, self.experts_per_rank
+        pairs_total = ep * cap_tokens * k
+        cap = pairs_total + per * (BLOCK_SIZE_M - 1)
+        i32 = dict(dtype=torch.int32, device=device)
+        bf16 = dict(dtype=torch.bfloat16, device=device)
+        try:
+            x_stage = PeerBuffer(cap_tokens * hidden * 2, device, self.group)
             try:
-                x_stage = PeerBuffer(cap_tokens * hidden * 2, device, self.group)
-                try:
-                    cache3 = PeerBuffer(cap_tokens * k * hidden * 2, device, self.group)
-                except PeerMemoryUnavailable:
-                    x_stage.close()
-                    raise
-            except PeerMemoryUnavailable as e:
-                # Every rank lands here together.  Forced peer mode has no other way; otherwise
-                # the NCCL exchange takes over for good.
-                if self.exchange == "peer":
-                    raise
-                import warnings
-                warnings.warn(f"ExpertParallelMoE: peer-memory exchange unavailable ({e}); "
-                              "using NCCL all-to-alls")
-                self.exchange = "nccl"
-                self._peer_states[key] = None
-                return None
-            state = {
-                "x_stage": x_stage, "cache3": cache3, "capacity": cap, "cap_tokens": cap_tokens,
-                "x_local": x_stage.local.view(torch.bfloat16).view(cap_tokens, hidden),
-                "c3_local": cache3.local.view(torch.bfloat16).view(cap_tokens, k, hidden),
-                # Own ids and weights padded to cap_tokens rows; -1 never matches an expert.
-                "ids_pad": torch.full((cap_tokens * k,), -1, **i32),
-                "w_pad": torch.zeros(cap_tokens * k, dtype=torch.float32, device=device),
-                "ids_all": torch.empty(pairs_total, **i32),
-                "w_all": torch.empty(pairs_total, dtype=torch.float32, device=device),
-                "sorted_ids": torch.empty(cap, **i32),
-                "expert_ids": torch.zeros((cap + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M, **i32),
-                "num_post_pad": torch.zeros(1, **i32),
-                "align_ws": torch.empty(max(_C.align_workspace_numel(pairs_total, per), 1), **i32),
-                "a_sorted": torch.empty(cap, hidden, **bf16),
-                "act": torch.empty(cap, self.intermediate_size, **bf16),
-                "token": torch.zeros(1, **i32),
-            }
+                cache3 = PeerBuffer(cap_tokens * k * hidden * 2, device, self.group)
+            except PeerMemoryUnavailable:
+                x_stage.close()
+                raise
+        except PeerMemoryUnavailable as e:
+            # Every rank lands here together.  Forced peer mode has no other way; otherwise
+            # the NCCL exchange takes over for good.
+            if self.exchange == "peer":
+                raise
+            import warnings
+            warnings.warn(f"ExpertParallelMoE: peer-memory exchange unavailable ({e}); "
+                          "using NCCL all-to-alls")
+            self.exchange = "nccl"
+            return None
+        state = {
+            "x_stage": x_stage, "cache3": cache3, "capacity": cap, "cap_tokens": cap_tokens,
+            "x_local": x_stage.local.view(torch.bfloat16).view(cap_tokens, hidden),
+            "c3_local": cache3.local.view(torch.bfloat16).view(cap_tokens, k, hidden),
+            # Own ids and weights padded to cap_tokens rows; -1 never matches an expert.
+            "ids_pad": torch.full((cap_tokens * k,), -1, **i32),
+            "w_pad": torch.zeros(cap_tokens * k, dtype=torch.float32, device=device),
+            "ids_all": torch.empty(pairs_total, **i32),
+            "w_all": torch.empty(pairs_total, dtype=torch.float32, device=device),
+            "sorted_ids": torch.empty(cap, **i32),
+            "expert_ids": torch.zeros((cap + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M, **i32),
+            "num_post_pad": torch.zeros(1, **i32),
+            "align_ws": torch.empty(max(_C.align_workspace_numel(pairs_total, per), 1), **i32),
+            "a_sorted": torch.empty(cap, hidden, **bf16),
+            "act": torch.empty(cap, self.intermediate_size, **bf16),
+            "token": torch.zeros(1, **i32),
+        }
         self._peer_states[key] = state
         return state
 
@@ -455,9 +510,8 @@ class ExpertParallelMoE(nn.Module):
         """Unmaps and frees the peer-visible buffers of the peer-memory exchange (every rank,
         after the last step has finished on every rank)."""
         for st in self._peer_states.values():
-            if st is not None:
-                st["x_stage"].close()
-                st["cache3"].close()
+            st["x_stage"].close()
+            st["cache3"].close()
         self._peer_states.clear()
 
     def _forward_peer(self, st: dict, hidden_states: torch.Tensor,
@@ -520,8 +574,6 @@ class ExpertParallelMoE(nn.Module):
                                   hidden_states.device)
             if st is not None:
                 return self._forward_peer(st, hidden_states, router_logits)
-            if self.exchange == "peer":
-                raise RuntimeError("exchange='peer' needs the same token count on every rank")
         ops, ep, per = self.ops, self.ep_size, self.experts_per_rank
         dev = hidden_states.device
         weights, ids = ops.route(router_logits, self.top_k, self.renormalize)

@@ -26,6 +26,87 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _worker_full_size(rank, port, mode, result_dir):
+    """BASELINE config 3 at its own size: Mixtral-8x7B shape, T=16384 per step on two GPUs.  Weights
+    and tokens are drawn on the device from the workload seed (both ranks draw the same values);
+    the oracle runs on a fixed sample of tokens."""
+    from electrock_infer_b200 import _lib
+    from electrock_infer_b200.layers.moe import FusedMoE, fused_experts
+    from electrock_infer_b200.parallel import ExpertParallelMoE
+    from electrock_infer_b200.synthetic import WORKLOADS
+    from oracle import moe_oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+    wl = WORKLOADS["mixtral_parallel_t16384"]
+    T, I = wl.num_tokens, wl.inter
+    full = make_inputs(wl, device=dev, device_rng=True)
+    res = {}
+    with torch.inference_mode():
+        if mode == "ep_full_size":
+            per = wl.num_experts // WORLD
+            layer = ExpertParallelMoE(8, 2, wl.hidden, I, params_dtype=torch.bfloat16,
+                                      max_tokens_per_rank=T // WORLD).to(dev)
+            layer.w13_weight.data.copy_(full["w13"][rank * per:(rank + 1) * per])
+            layer.w2_weight.data.copy_(full["w2"][rank * per:(rank + 1) * per])
+            lo, hi = rank * T // WORLD, (rank + 1) * T // WORLD
+        else:
+            shard = I // WORLD
+            layer = FusedMoE(8, 2, wl.hidden, I, tp_size=WORLD, params_dtype=torch.bfloat16,
+                             reduce_results=True, tp_exchange="peer").to(dev)
+            for e in range(8):
+                layer.weight_loader(layer.w13_weight, full["w13"][e, :I], "w1", e)
+                layer.weight_loader(layer.w13_weight, full["w13"][e, I:], "w3", e)
+                layer.weight_loader(layer.w2_weight, full["w2"][e], "w2", e)
+            assert layer.w13_weight.shape[1] == 2 * shard
+            lo, hi = 0, T
+        x = full["x"][lo:hi].clone()
+        out = layer(x, full["logits"][lo:hi].contiguous())
+        torch.cuda.synchronize()
+        res["alias"] = out.data_ptr() == x.data_ptr()
+        single = fused_experts(full["x"][lo:hi].clone(), full["w13"], full["w2"],
+                               full["logits"][lo:hi].contiguous(), 2, inplace=True)
+        torch.cuda.synchronize()
+        res["bit_exact_vs_single"] = bool(torch.equal(out, single))
+        res["vs_single"] = moe_oracle.error_stats(out.float().cpu(), single.float().cpu())
+        sample = torch.randperm(hi - lo, generator=torch.Generator().manual_seed(rank))[:64].to(dev)
+        want = moe_oracle.moe_block_ref(full["x"][lo:hi][sample].cpu(), full["w13"].cpu(),
+                                        full["w2"].cpu(), full["logits"][lo:hi][sample].cpu())
+        res["stats"] = moe_oracle.error_stats(out[sample].float().cpu(), want)
+        if mode == "tp_full_size":
+            both = [torch.empty_like(out) for _ in range(WORLD)]
+            dist.all_gather(both, out)
+            res["ranks_agree"] = bool(torch.equal(both[0], both[1]))
+    res["gemm_status"] = _lib.load().b200moe_gemm_device_status(1)
+    dist.barrier()
+    if mode == "ep_full_size":
+        layer.close()
+    else:
+        layer._tp_reduce.close()
+    torch.save(res, os.path.join(result_dir, f"{mode}{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["ep_full_size", "tp_full_size"])
+def test_two_gpu_layer_at_config_size(tmp_path, mode):
+    """T=16384 at Mixtral shape, expert parallel over peer memory and tensor parallel with the
+    in-kernel reduce: in-place result, oracle on a 64-token sample per rank, and against the
+    single-GPU layer on the same rows (bit for bit for EP)."""
+    if torch.cuda.device_count() < WORLD:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_worker_full_size, args=(_free_port(), mode, str(tmp_path)), nprocs=WORLD, join=True)
+    for rank in range(WORLD):
+        r = torch.load(tmp_path / f"{mode}{rank}.pt")
+        assert r["alias"] and r["gemm_status"] == 0, r
+        assert r["stats"]["max_abs"] <= 3e-2 and r["stats"]["rel_fro"] <= 1e-2, r
+        if mode == "ep_full_size":
+            assert r["bit_exact_vs_single"], "expert-parallel rows must equal the single-GPU rows"
+        else:
+            assert r["vs_single"]["rel_fro"] <= 1e-2 and r["ranks_agree"], r
+
+
 def _worker(rank, port, mode, result_dir):
     from electrock_infer_b200 import _lib
     from electrock_infer_b200.layers.moe import FusedMoE, fused_experts
@@ -101,9 +182,12 @@ def _worker(rank, port, mode, result_dir):
         torch.cuda.synchronize()
         res["bit_exact_second_call"] = bool(torch.equal(out2, single[lo:hi])) and out2.shape[0] == hi - lo
     else:
+        # "auto" takes the peer-memory exchange only with a bound on the tokens per rank.
         layer = ExpertParallelMoE(8, 2, wl.hidden, wl.inter, params_dtype=torch.bfloat16,
                                   exchange="peer" if mode.startswith("ep_peer") else
-                                  ("auto" if mode == "ep_auto_fallback" else "nccl")).to(dev)
+                                  ("auto" if mode == "ep_auto_fallback" else "nccl"),
+                                  max_tokens_per_rank=tokens // 2 if mode == "ep_auto_fallback"
+                                  else None).to(dev)
         for e in range(8):
             layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter].to(dev), "w1", e)
             layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:].to(dev), "w3", e)

@@ -50,7 +50,7 @@ class OracleOps:
     def combine(self, y_back, order, out, top_k):
         cache = torch.zeros(out.shape[0] * top_k, out.shape[1], dtype=y_back.dtype)
         cache[order.long()] = y_back
-        out.copy_(cache.view(out.shape[0], top_k, -1).float().sum(1).to(out.dtype))
+        out.copy_(cache.view(out.shape[0], top_k, out.shape[1]).float().sum(1).to(out.dtype))
 
 
 def _free_port():
@@ -150,6 +150,61 @@ def test_tensor_parallel_all_reduce_on_gloo(tmp_path):
     for rank in range(WORLD):
         r = torch.load(tmp_path / f"tp{rank}.pt")
         assert r["alias"] and r["err"] < 1e-4 and r["refused"], r
+
+
+def _decision_worker(rank, port, result_dir):
+    """Which exchange a call takes must not depend on anything only one rank can see.  The ranks
+    walk through batches whose sizes change unevenly between calls (the case in which a choice
+    keyed on the local token count sent the ranks into different collectives) and record, call by
+    call, what ``peer_capacity`` answers; with the oracle stand-in every call then runs the NCCL
+    exchange to the end, which would hang if the ranks disagreed."""
+    from electrock_infer_b200.parallel import ExpertParallelMoE, TensorParallelReduce
+    _init(rank, port)
+    wl = MoEWorkload("ep", 100, 32, 64, dtype=torch.float32, seed=5)
+    full = make_inputs(wl)
+    counts = [(50, 50), (50, 45), (50, 50), (10, 0), (0, 30), (50, 50)]  # (rank 0, rank 1) per call
+    seen = {}
+    for name, kwargs in (("auto", {}), ("auto_bounded", {"max_tokens_per_rank": 64}),
+                         ("nccl", {"exchange": "nccl"}),
+                         ("peer_bounded", {"exchange": "peer", "max_tokens_per_rank": 64})):
+        layer = ExpertParallelMoE(wl.num_experts, 2, wl.hidden, wl.inter, params_dtype=torch.float32,
+                                  ops=OracleOps(), **kwargs)
+        for e in range(wl.num_experts):
+            layer.weight_loader(layer.w13_weight, full["w13"][e, : wl.inter], "w1", e)
+            layer.weight_loader(layer.w13_weight, full["w13"][e, wl.inter:], "w3", e)
+            layer.weight_loader(layer.w2_weight, full["w2"][e], "w2", e)
+        answers = []
+        for pair in counts:
+            n = pair[rank]
+            answers.append(layer.peer_capacity(n))
+            lo = 0 if rank == 0 else 50
+            out = layer(full["x"][lo:lo + n].clone(), full["logits"][lo:lo + n])
+            assert out.shape[0] == n
+        seen[name] = answers
+    # Forced peer mode without a bound: the caller promises equal counts; the capacity is a bucket.
+    forced = ExpertParallelMoE(wl.num_experts, 2, wl.hidden, wl.inter, params_dtype=torch.float32,
+                               ops=OracleOps(), exchange="peer")
+    seen["peer_unbounded"] = [forced.peer_capacity(n) for n in (1, 256, 257, 2048, 3000)]
+    red = TensorParallelReduce()
+    seen["tp_capacity"] = [red.capacity_for(n) for n in (2, 600, 8192, 8194)]
+    torch.save(seen, os.path.join(result_dir, f"dec{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_exchange_choice_is_the_same_on_every_rank(tmp_path):
+    mp.spawn(_decision_worker, args=(_free_port(), str(tmp_path)), nprocs=WORLD, join=True)
+    a, b = (torch.load(tmp_path / f"dec{r}.pt") for r in range(WORLD))
+    assert a == b, (a, b)
+    assert a["auto"] == [None] * 6 and a["nccl"] == [None] * 6
+    assert a["auto_bounded"] == [64] * 6 and a["peer_bounded"] == [64] * 6
+    assert a["peer_unbounded"] == [256, 256, 512, 2048, 4096]
+    assert a["tp_capacity"] == [256, 1024, 8192, 16384]
+
+
+def test_workspace_capacity_buckets():
+    from electrock_infer_b200.layers.moe.fused_moe import capacity_bucket
+    assert [capacity_bucket(n) for n in (0, 1, 255, 256, 257, 8191, 8192, 8193)] == \
+        [256, 256, 256, 256, 512, 8192, 8192, 16384]
 
 
 def test_split_sizes_and_row_experts():
