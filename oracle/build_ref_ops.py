@@ -1,6 +1,7 @@
 """Oracle build of the reference's own CUDA MoE ops.  TEST INFRASTRUCTURE ONLY.
 
     python oracle/build_ref_ops.py /path/to/electrock-infer
+    ELECTROCK_REFERENCE=/path/to/electrock-infer python oracle/build_ref_ops.py
 
 Compiles, from where they lie in the reference source tree and without modifying or copying them,
 src/{topk_softmax_kernels,moe_align_block_size,activation_kernels,moe_sum,moe_sum_efficient}.cu
@@ -16,6 +17,7 @@ of its input unless the token count is a multiple of 4 (src/topk_softmax_kernels
 """
 from __future__ import annotations
 
+import os
 import subprocess
 import sys
 import sysconfig
@@ -28,7 +30,12 @@ SOURCES = ["topk_softmax_kernels.cu", "moe_align_block_size.cu", "activation_ker
 
 
 def main() -> int:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ELECTROCK_REFERENCE")
+    if not where:
+        print("give the path of the electrock-infer source tree as the first argument or in "
+              "ELECTROCK_REFERENCE; nothing built")
+        return 2
+    ref_root = Path(where)
     src_dir = ref_root / "src"
     if not all((src_dir / s).exists() for s in SOURCES):
         print(f"reference sources not found under {src_dir}; nothing built")

@@ -133,3 +133,35 @@ def test_package_surface():
     for name in ("topk_softmax", "moe_align_block_size", "silu_and_mul", "moe_sum",
                  "moe_sum_efficient"):
         assert callable(getattr(_C, name))
+
+
+def test_install_into_reference_replaces_the_layer_everywhere():
+    """``install_into_reference()`` against the reference's real package (the copy staged by
+    oracle/stage_reference_python.py, or the tree ELECTROCK_REFERENCE names): the model module,
+    which binds ``FusedMoE`` by name when the package is imported, must end up holding this
+    library's class, and the reference's ``_C`` must be this library's op module.  Runs in a child
+    interpreter so that the reference package does not stay imported in the test process."""
+    import os
+    import subprocess
+    import sys
+    repo = Path(__file__).resolve().parent.parent
+    staged = repo / "oracle" / "_ref" / "reference_python"
+    where = staged if (staged / "electrock_infer").is_dir() else os.environ.get("ELECTROCK_REFERENCE")
+    if not where or not (Path(where) / "electrock_infer").is_dir():
+        pytest.skip("the reference's Python package is not available on this machine")
+    code = (
+        "import sys; sys.dont_write_bytecode = True\n"
+        f"sys.path.insert(0, {str(repo)!r}); sys.path.insert(0, {str(where)!r})\n"
+        "import electrock_infer_b200 as ours\n"
+        "replaced = ours.install_into_reference()\n"
+        "import electrock_infer, electrock_infer.models.mixtral as model\n"
+        "import electrock_infer.layers.moe.mixtral_moe as layer, electrock_infer.layers.moe.fused_moe as fused\n"
+        "from electrock_infer_b200.layers.moe import FusedMoE, fused_experts, fused_topk\n"
+        "from electrock_infer_b200 import _C\n"
+        "assert model.FusedMoE is FusedMoE and layer.FusedMoE is FusedMoE, replaced\n"
+        "assert layer.fused_experts is fused_experts and fused.fused_experts is fused_experts\n"
+        "assert fused.fused_topk is fused_topk and electrock_infer._C is _C and fused._C is _C\n"
+        "assert 'electrock_infer.models.mixtral' in replaced\n"
+        "print('ok')\n")
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0 and proc.stdout.strip().endswith("ok"), proc.stderr[-2000:]
