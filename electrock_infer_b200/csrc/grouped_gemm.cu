@@ -287,7 +287,20 @@ struct GemmParams {
   int m_group;                   // M blocks per L2-resident group of an expert (0: no grouping)
   int top_k;                     // kW13Gather: A row of slot s is sorted[s] / top_k
   int num_src_rows;              // kW13Gather: rows of the token tensor
+  int dual_min_blocks;           // > 0: the one-block and the two-block kernel are both launched and
+                                 // decide on the device which of them runs (two_block_tiles_win)
 };
+
+// The choice between one and two M blocks per tile, made on the device from the real block counts
+// (the host only knows an upper bound of the rows, and under expert parallelism that bound is the
+// whole batch while a rank receives a fraction of it).  Both kernels of a launch pair evaluate
+// it on the same counts; exactly one of them does the work, the other returns after its prologue.
+__device__ __forceinline__ bool two_block_tiles_win(const int* blk_off, int num_experts,
+                                                    int min_blocks_per_expert) {
+  int busy = 0;
+  for (int e = 0; e < num_experts; ++e) busy += blk_off[e + 1] > blk_off[e] ? 1 : 0;
+  return busy > 0 && blk_off[num_experts] >= min_blocks_per_expert * busy;
+}
 
 
 // ------------------------------------------------------------------------------ epilogue bodies
@@ -486,7 +499,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  const long long total_tiles = static_cast<long long>(s_blk_off[p.num_experts]) * p.n_tiles;
+  long long total_tiles = static_cast<long long>(s_blk_off[p.num_experts]) * p.n_tiles;
+  if (p.dual_min_blocks > 0 && two_block_tiles_win(s_blk_off, p.num_experts, p.dual_min_blocks))
+    total_tiles = 0;  // the two-block kernel launched beside this one does the work
   volatile int* abort_flag = &s_abort;
 
   constexpr bool kIsW13 = (kMode != kW2);
@@ -660,14 +675,15 @@ constexpr int kDualStages = 3;
 constexpr int kDualABytes = 2 * kABytes;                      // 32768: 256 rows x 64 columns
 constexpr int kDualStageBytes = kDualABytes + kBBytes;        // 65536
 constexpr int kDualSmemBytes = kDualStages * kDualStageBytes + kOutStageBytes + kSmemAlignSlack;
-// Batch size from which the two-block kernel is chosen, in average M blocks per expert.  Measured
-// on B200 at Mixtral shape, interleaved runs: the second GEMM (K = 14336, epilogue negligible)
-// gains 3-10 % at T = 8192 and 10 % at T = 16384 and loses below about six blocks per expert,
-// where the round-robin deal of tiles that cost one or two units leaves CTAs idle; the first GEMM
-// (K = 4096, so the drain that no longer overlaps the next tile's MMAs weighs more) gains 3-4 % at
-// T = 16384 and nothing at T = 8192.
+// Batch size from which the two-block kernel is chosen, in average M blocks per expert that has
+// any (counted on the device, see two_block_tiles_win).  Measured on B200 at Mixtral shape,
+// interleaved runs: the second GEMM (K = 14336, epilogue negligible) gains 8-10 % at T = 8192 and
+// T = 16384 and loses below about six blocks per expert, where the round-robin deal of tiles that
+// cost one or two units leaves CTAs idle (T = 2048 with skewed routing: -13 %); the first GEMM
+// (K = 4096, so the part of the drain that no longer overlaps the next tile's MMAs weighs more)
+// gains 3-4 % at T = 8192 and T = 16384 and nothing at T = 2048.
 constexpr int kDualMinBlocksPerExpertW2 = 6;
-constexpr int kDualMinBlocksPerExpertW13 = 24;
+constexpr int kDualMinBlocksPerExpertW13 = 12;
 
 struct DualTile {
   int expert;
@@ -785,6 +801,8 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
   seq.num_experts = p.num_experts;
   seq.unit_group = p.m_group > 0 ? (p.m_group + 1) / 2 : 0;
   seq.total = static_cast<long long>(s_unit_off[p.num_experts]) * p.n_tiles;
+  if (p.dual_min_blocks > 0 && !two_block_tiles_win(s_blk_off, p.num_experts, p.dual_min_blocks))
+    seq.total = 0;  // the one-block kernel launched beside this one does the work
   seq.cut = seq.total - seq.total % gridDim.x;
   if (2 * (seq.total - seq.cut) > static_cast<long long>(gridDim.x)) seq.cut = seq.total;
 
@@ -1347,12 +1365,27 @@ std::atomic<int> g_tiling{0};
 // shared by two blocks almost everywhere.  With one block per expert (decode-sized batches) every
 // tile would be a one-block tile without the double-buffered accumulator, so the one-block kernel
 // is kept there.  `capacity` = pairs + num_experts * 127 bounds the padded row count.
-bool use_two_block_tiles(int64_t capacity, int num_experts, int min_blocks_per_expert) {
+enum TileChoice { kOneBlock, kTwoBlock, kDecideOnDevice };
+
+// kOneBlock when even the upper bound of the rows is too small for two-block tiles to pay (only
+// the one-block kernel is launched); kDecideOnDevice otherwise: both kernels are launched and the
+// real block counts decide (GemmParams::dual_min_blocks).
+TileChoice choose_tiles(int64_t capacity, int num_experts, int min_blocks_per_expert) {
   const int mode = g_tiling.load(std::memory_order_relaxed);
-  if (capacity < 2 * kBlockM) return false;
-  if (mode != 0) return mode == 2;
+  if (capacity < 2 * kBlockM || mode == 1) return kOneBlock;
+  if (mode == 2) return kTwoBlock;
   const int64_t pairs = capacity - static_cast<int64_t>(num_experts) * (kBlockM - 1);
-  return pairs >= static_cast<int64_t>(num_experts) * kBlockM * min_blocks_per_expert;
+  return pairs >= static_cast<int64_t>(kBlockM) * min_blocks_per_expert ? kDecideOnDevice : kOneBlock;
+}
+
+template <int kMode>
+int launch_chosen(TileChoice choice, int min_blocks, const CUtensorMap& ta, const CUtensorMap& ta2,
+                  const CUtensorMap& tb, GemmParams p, cudaStream_t st) {
+  if (choice == kOneBlock) return launch<kMode>(ta, tb, p, st);
+  if (choice == kTwoBlock) return launch_dual<kMode>(ta, ta2, tb, p, st);
+  p.dual_min_blocks = min_blocks;
+  if (int rc = launch<kMode>(ta, tb, p, st)) return rc;
+  return launch_dual<kMode>(ta, ta2, tb, p, st);
 }
 
 template <int kMode>
@@ -1445,8 +1478,10 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   if (!aligned_to(a_sorted, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
   // The two-CTA kernel has a fixed 128 + 128 column tile; the one-CTA kernels pick their width.
-  const bool two_block = block_m == kBlockM &&
-                         use_two_block_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW13);
+  const TileChoice tiles = block_m == kBlockM
+                               ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW13)
+                               : kOneBlock;
+  const bool two_block = tiles != kOneBlock;
   const int half_n = block_m == kPairBlockM ? kBlockN / 2
                                             : choose_half_n(sorted_capacity, num_experts, inter);
   CUtensorMap ta, ta2, tb;
@@ -1471,8 +1506,8 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   set_width(&p, 2 * half_n);
   p.m_group = m_group_for(hidden * 2);
   if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  if (two_block) return launch_dual<kW13>(ta, ta2, tb, p, static_cast<cudaStream_t>(stream));
-  return launch<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW13>(tiles, kDualMinBlocksPerExpertW13, ta, ta2, tb, p,
+                             static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w13_swiglu_gather(
@@ -1546,8 +1581,10 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16) || !aligned_to(out, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  const bool two_block = block_m == kBlockM &&
-                         use_two_block_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2);
+  const TileChoice tiles = block_m == kBlockM
+                               ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2)
+                               : kOneBlock;
+  const bool two_block = tiles != kOneBlock;
   CUtensorMap ta, ta2, tb;
   if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
   if (two_block)
@@ -1573,8 +1610,8 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  if (two_block) return launch_dual<kW2>(ta, ta2, tb, p, static_cast<cudaStream_t>(stream));
-  return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, ta2, tb, p,
+                            static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w2_scale_peer(
@@ -1599,8 +1636,10 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  const bool two_block = block_m == kBlockM &&
-                         use_two_block_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2);
+  const TileChoice tiles = block_m == kBlockM
+                               ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2)
+                               : kOneBlock;
+  const bool two_block = tiles != kOneBlock;
   CUtensorMap ta, ta2, tb;
   if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
   if (two_block)
@@ -1627,8 +1666,8 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  if (two_block) return launch_dual<kW2>(ta, ta2, tb, p, static_cast<cudaStream_t>(stream));
-  return launch<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, ta2, tb, p,
+                            static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_gemm_set_tiling(int mode) {

@@ -196,6 +196,26 @@ class _timed:
         return False
 
 
+_bf16_weight_copies: Dict[tuple, torch.Tensor] = {}
+
+
+def _bf16_weights(w: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of an fp16/fp32 weight tensor, made once per (storage, version): the grouped GEMMs
+    read bf16 operands only."""
+    if w.dtype == torch.bfloat16:
+        return w
+    key = (w.data_ptr(), w._version, tuple(w.shape), w.dtype)
+    hit = _bf16_weight_copies.get(key)
+    if hit is None:
+        for old in [k for k in _bf16_weight_copies if k[0] == key[0]]:
+            del _bf16_weight_copies[old]   # the parameter changed: drop the stale copy
+        if len(_bf16_weight_copies) >= 64:
+            _bf16_weight_copies.pop(next(iter(_bf16_weight_copies)))
+        hit = w.detach().to(torch.bfloat16).contiguous()
+        _bf16_weight_copies[key] = hit
+    return hit
+
+
 def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
                   gating_output: Optional[torch.Tensor], topk: int, renormalize: bool = True,
                   inplace: bool = False, activation: str = "silu",
@@ -205,7 +225,14 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
     ``w1`` is the stacked gate/up weight ``[E, 2*I, H]`` (gate rows first), ``w2`` is
     ``[E, H, I]``, ``gating_output`` the router logits ``[T, E]`` in any float dtype.  With
     ``inplace`` the result overwrites and aliases ``hidden_states``, as the layer relies on.
-    Tensors must be bf16 on a CUDA device: there is no other implementation behind this call.
+    Tensors must be on a CUDA device: there is no other implementation behind this call.
+
+    Element types: the reference takes any float dtype and computes in bf16 whatever it is given
+    (``compute_type=tl.bfloat16``, fused_moe.py:254,286).  Here bf16 tensors are the native case.
+    fp16 or fp32 ``hidden_states`` are converted to bf16 on entry and the result is converted back
+    into a tensor of the caller's dtype (into ``hidden_states`` itself with ``inplace``); fp16 or
+    fp32 weights are converted once and the bf16 copy is kept until the parameter changes
+    (``_bf16_weights``), which doubles their memory: load bf16 weights where that matters.
 
     Extension: with ``gate_weight`` (bf16 ``[E, H]``) the gate projection is computed by the router
     kernel itself and ``gating_output`` may be ``None``.  With ``tp_reduce`` (a
@@ -217,9 +244,19 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
         raise NotImplementedError(f"Activation {activation} not supported.")
     if not hidden_states.is_cuda:
         raise RuntimeError("fused_experts: tensors must be on a CUDA device; no CPU path exists")
-    if not (hidden_states.dtype == w1.dtype == w2.dtype == torch.bfloat16):
-        raise RuntimeError("fused_experts: hidden_states, w1 and w2 must be bfloat16 "
+    floats = (torch.bfloat16, torch.float16, torch.float32)
+    if hidden_states.dtype not in floats or w1.dtype not in floats or w2.dtype not in floats:
+        raise RuntimeError("fused_experts: hidden_states, w1 and w2 must be bf16, fp16 or fp32 "
                            f"(got {hidden_states.dtype}, {w1.dtype}, {w2.dtype})")
+    if w1.dtype != torch.bfloat16 or w2.dtype != torch.bfloat16:
+        w1, w2 = _bf16_weights(w1), _bf16_weights(w2)
+    if hidden_states.dtype != torch.bfloat16:
+        # Compute in bf16 like the reference, hand the result back in the caller's dtype.
+        result = fused_experts(hidden_states.to(torch.bfloat16), w1, w2, gating_output, topk,
+                               renormalize, True, activation, gate_weight, tp_reduce)
+        if inplace:
+            return hidden_states.copy_(result)
+        return result.to(hidden_states.dtype)
     num_tokens, hidden = hidden_states.shape
     num_experts, inter_x2, w1_k = w1.shape
     inter = inter_x2 // 2

@@ -245,11 +245,17 @@ class TensorParallelReduce:
 class CudaOps:
     """The arithmetic steps of the expert-parallel layer on the local GPU (C-ABI calls)."""
 
-    def route(self, logits: torch.Tensor, top_k: int,
-              renormalize: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    def route(self, logits: torch.Tensor, top_k: int, renormalize: bool,
+              out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Routing weights (fp32) and expert ids (int32), ``[T, top_k]`` each; written into the
+        tensors of ``out`` when given."""
         T = logits.shape[0]
-        w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
-        ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+        if out is not None:
+            w, ids = out
+        else:
+            w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+            ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
         with _timed("topk_softmax"):
             _C.topk_softmax(w, ids, logits.contiguous(), renormalize=renormalize)
         return w, ids
@@ -490,10 +496,10 @@ class ExpertParallelMoE(nn.Module):
             "x_stage": x_stage, "cache3": cache3, "capacity": cap, "cap_tokens": cap_tokens,
             "x_local": x_stage.local.view(torch.bfloat16).view(cap_tokens, hidden),
             "c3_local": cache3.local.view(torch.bfloat16).view(cap_tokens, k, hidden),
-            # Own ids and weights padded to cap_tokens rows; -1 never matches an expert.
-            "ids_pad": torch.full((cap_tokens * k,), -1, **i32),
-            "w_pad": torch.zeros(cap_tokens * k, dtype=torch.float32, device=device),
-            "ids_all": torch.empty(pairs_total, **i32),
+            # Own routing result, padded to cap_tokens rows: row 0 the expert ids (-1 never matches
+            # an expert), row 1 the bits of the fp32 routing weights.  One all-gather moves both.
+            "own": torch.full((2, cap_tokens * k), -1, **i32),
+            "all": torch.empty(ep, 2, cap_tokens * k, **i32),
             "w_all": torch.empty(pairs_total, dtype=torch.float32, device=device),
             "sorted_ids": torch.empty(cap, **i32),
             "expert_ids": torch.zeros((cap + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M, **i32),
@@ -524,21 +530,20 @@ class ExpertParallelMoE(nn.Module):
         if num_tokens > cap_tokens:
             raise RuntimeError(f"ExpertParallelMoE: {num_tokens} tokens exceed max_tokens_per_rank="
                                f"{cap_tokens}")
-        weights, ids = self.ops.route(router_logits, k, self.renormalize)
+        own = st["own"]
+        if num_tokens < cap_tokens:  # a short batch: rows past num_tokens carry ids the alignment skips
+            own[0, num_tokens * k:].fill_(-1)
+        if num_tokens > 0:  # the router writes straight into the buffer that is exchanged
+            self.ops.route(router_logits, k, self.renormalize,
+                           out=(own[1, : num_tokens * k].view(torch.float32).view(num_tokens, k),
+                                own[0, : num_tokens * k].view(num_tokens, k)))
         with _timed("copy:stage_tokens"):
             st["x_local"][:num_tokens].copy_(hidden_states)
-        if num_tokens == cap_tokens:
-            ids_own, w_own = ids.view(-1), weights.view(-1)
-        else:  # a short batch: rows past num_tokens carry pair indices the alignment skips
-            ids_own, w_own = st["ids_pad"], st["w_pad"]
-            ids_own.fill_(-1)
-            ids_own[: num_tokens * k].copy_(ids.view(-1))
-            w_own[: num_tokens * k].copy_(weights.view(-1))
-        # The all-gathers also order every rank's staging copy before any rank's gather.
+        # The all-gather also orders every rank's staging copy before any rank's gather.
         with _timed("all_gather:ids_weights"):
-            dist.all_gather_into_tensor(st["ids_all"], ids_own, group=self.group)
-            dist.all_gather_into_tensor(st["w_all"], w_own, group=self.group)
-        local_ids = st["ids_all"] - self.first_expert  # other ranks' experts fall outside [0, per)
+            dist.all_gather_into_tensor(st["all"], own, group=self.group)
+        local_ids = st["all"][:, 0, :] - self.first_expert  # other ranks' experts fall outside [0, per)
+        st["w_all"].view(ep, cap_tokens * k).copy_(st["all"][:, 1, :].view(torch.float32))
         stream = torch.cuda.current_stream(dev).cuda_stream
         with _timed("moe_align_block_size"):
             _C.moe_align_block_size(local_ids, per, BLOCK_SIZE_M, st["sorted_ids"], st["expert_ids"],

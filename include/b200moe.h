@@ -397,8 +397,8 @@ int b200moe_gemm_device_status(int reset);
  * Tiling of the one-CTA grouped GEMMs (block_m = 128), a process-wide setting for benchmarks and
  * tests: 0 (default) chooses by batch size, 1 forces one 128-row M block per tile (128 x 256
  * accumulator, double-buffered in tensor memory), 2 forces two M blocks of one expert per tile
- * (they share every weight stage; chosen by default for the second GEMM from about six M blocks
- * per expert on and for the first from about twenty-four).
+ * (they share every weight stage; chosen by default, on the device from the real block counts,
+ * for the second GEMM from about six M blocks per expert on and for the first from about twelve).
  * All tilings produce the same bits.  The reference's counterpart is the tile configuration table
  * of layers/moe/fused_moe.py:327-339.  Returns 0 or B200MOE_ERR_SHAPE.
  */
