@@ -71,7 +71,10 @@ SIGNATURES = {
     "b200moe_peer_close": (c_int, [c_void_p]),
     "b200moe_peer_free": (c_int, [c_void_p]),
     "b200moe_gemm_device_status": (c_int, [c_int]),
+    "b200moe_gemm_measured_cycles": (c_int, [c_void_p, c_int]),
     "b200moe_gemm_set_tiling": (c_int, [c_int]),
+    "b200moe_gemm_two_block_schedule": (c_int64, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                  c_void_p, c_int64]),
 }
 
 _lib = None

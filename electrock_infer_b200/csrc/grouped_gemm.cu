@@ -68,6 +68,22 @@ enum Mode { kW13 = 0, kW2 = 1, kW13Gather = 2 };
 // Device status word: 0 = fine; otherwise (role << 8) | barrier kind of the wait that ran out.
 __device__ int g_gemm_status = 0;
 
+// Cycle accounting of the two-block kernel, compiled in with -DB200MOE_MEASURE_CYCLES only (a
+// measurement build: the counters cost a few clock reads per K step).  Summed over all CTAs:
+//   [0] cycles epilogue warp 2 spent draining accumulators   [1] accumulators drained by it
+//   [2] cycles the MMA thread waited for operand stages       [3] ... for a free accumulator
+//   [4] cycles the MMA thread spent in its tile loop          [5] items (tiles) it processed
+//   [6], [7] the part of [2] spent in the first / the last kDualStages K steps of two-block tiles
+// Read and cleared by b200moe_gemm_measured_cycles().
+__device__ unsigned long long g_gemm_cycles[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#ifdef B200MOE_MEASURE_CYCLES
+#define B200MOE_CYCLES_BEGIN(var) const long long var = clock64()
+#define B200MOE_CYCLES_ADD(acc, var) acc += clock64() - var
+#else
+#define B200MOE_CYCLES_BEGIN(var)
+#define B200MOE_CYCLES_ADD(acc, var)
+#endif
+
 // ------------------------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -321,19 +337,44 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return g * r * u;
 }
 
-// 16 gate and 16 up accumulator columns of this lane's row -> 16 bf16 outputs in the staging row.
-__device__ __forceinline__ void swiglu_chunk(const uint32_t (&g)[16], const uint32_t (&u)[16],
+// N gate and N up accumulator columns of this lane's row -> N bf16 outputs in the staging row.
+template <int N>
+__device__ __forceinline__ void swiglu_chunk(const uint32_t (&g)[N], const uint32_t (&u)[N],
                                              uint8_t* stage_row) {
-  uint32_t o[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    o[i] = pack_bf16(silu_mul(__uint_as_float(g[2 * i]), __uint_as_float(u[2 * i])),
-                     silu_mul(__uint_as_float(g[2 * i + 1]), __uint_as_float(u[2 * i + 1])));
   uint4* s4 = reinterpret_cast<uint4*>(stage_row);
-  s4[0] = make_uint4(o[0], o[1], o[2], o[3]);
-  s4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+  for (int q = 0; q < N / 8; ++q) {
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      o[i] = pack_bf16(silu_mul(__uint_as_float(g[8 * q + 2 * i]), __uint_as_float(u[8 * q + 2 * i])),
+                       silu_mul(__uint_as_float(g[8 * q + 2 * i + 1]), __uint_as_float(u[8 * q + 2 * i + 1])));
+    s4[q] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
 }
 
+// Writes `width` (<= 64, a multiple of 8) staged columns of the warp's 32 rows to consecutive rows
+// of the output, eight lanes per row.
+__device__ __forceinline__ void flush_rows(const uint8_t* stage_out, __nv_bfloat16* dst, long long ld,
+                                           int width, int lane) {
+  __syncwarp();
+  const int piece = lane & 7;
+  if (piece * 8 < width) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + (lane >> 3);
+      const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
+      *reinterpret_cast<uint4*>(dst + static_cast<long long>(r) * ld + piece * 8) = o;
+    }
+  }
+  __syncwarp();
+}
+
+// A tensor-memory load takes several hundred cycles to return while the MMAs are running
+// (measured: a drain that waited for every 16-column pair of loads took 4400 cycles per
+// accumulator, twice the time its arithmetic needs).  So 32 gate and 32 up columns are loaded at
+// a time into one of two register sets, and the next set's loads are in flight while the current
+// one goes through the special-function unit.
 __device__ __forceinline__ void drain_w13(const GemmParams& p, uint32_t taddr, uint8_t* stage_out,
                                           int m_block, int n_tile, int quarter, int lane) {
 #ifdef B200MOE_MEASURE_WITHOUT_EPILOGUE  // measurement builds only: results are not written
@@ -343,44 +384,37 @@ __device__ __forceinline__ void drain_w13(const GemmParams& p, uint32_t taddr, u
       (static_cast<long long>(m_block) * kBlockM + quarter * 32) * p.out_ld +
       static_cast<long long>(n_tile) * p.half_n;
   uint8_t* my_row = stage_out + lane * kOutStageRowBytes;
-  const int chunks = p.half_n >> 4;  // 16 gate columns (and their 16 up columns) per chunk
-  // Two register buffers: the tensor-memory loads of the next chunk are in flight while the
-  // current one goes through the special-function unit.
-  uint32_t ga[16], ua[16], gb[16], ub[16];
-  tmem_ld_32x16(taddr, ga);
-  tmem_ld_32x16(taddr + p.half_n, ua);
+  const int wide = p.half_n >> 5;  // chunks of 32 columns; a 16-column remainder may follow
+  uint32_t ga[32], ua[32], gb[32], ub[32];
+  if (wide > 0) {
+    tmem_ld_32x32(taddr, ga);
+    tmem_ld_32x32(taddr + p.half_n, ua);
+  }
 #pragma unroll 1
-  for (int j = 0; j < chunks; j += 2) {
+  for (int j = 0; j < wide; j += 2) {
     tmem_ld_wait();
-    if (j + 1 < chunks) {
-      tmem_ld_32x16(taddr + (j + 1) * 16, gb);
-      tmem_ld_32x16(taddr + p.half_n + (j + 1) * 16, ub);
+    if (j + 1 < wide) {
+      tmem_ld_32x32(taddr + (j + 1) * 32, gb);
+      tmem_ld_32x32(taddr + p.half_n + (j + 1) * 32, ub);
     }
-    swiglu_chunk(ga, ua, my_row + (j & 3) * 32);
-    if (j + 1 < chunks) {
+    swiglu_chunk<32>(ga, ua, my_row);
+    if (j + 1 < wide) {
       tmem_ld_wait();
-      if (j + 2 < chunks) {
-        tmem_ld_32x16(taddr + (j + 2) * 16, ga);
-        tmem_ld_32x16(taddr + p.half_n + (j + 2) * 16, ua);
+      if (j + 2 < wide) {
+        tmem_ld_32x32(taddr + (j + 2) * 32, ga);
+        tmem_ld_32x32(taddr + p.half_n + (j + 2) * 32, ua);
       }
-      swiglu_chunk(gb, ub, my_row + ((j + 1) & 3) * 32);
+      swiglu_chunk<32>(gb, ub, my_row + 64);
     }
-    if (((j + 2) & 3) == 0 || j + 2 >= chunks) {
-      // Up to 64 staged columns go out, eight lanes per row.
-      const int c0 = (j & ~3) * 16;
-      const int width = min(64, p.half_n - c0);
-      __syncwarp();
-      const int piece = lane & 7;
-      if (piece * 8 < width) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int r = i * 4 + (lane >> 3);
-          const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
-          *reinterpret_cast<uint4*>(tile_dst + static_cast<long long>(r) * p.out_ld + c0 + piece * 8) = o;
-        }
-      }
-      __syncwarp();
-    }
+    flush_rows(stage_out, tile_dst + j * 32, p.out_ld, j + 1 < wide ? 64 : 32, lane);
+  }
+  if (p.half_n & 16) {
+    uint32_t g[16], u[16];
+    tmem_ld_32x16(taddr + wide * 32, g);
+    tmem_ld_32x16(taddr + p.half_n + wide * 32, u);
+    tmem_ld_wait();
+    swiglu_chunk<16>(g, u, my_row);
+    flush_rows(stage_out, tile_dst + wide * 32, p.out_ld, 16, lane);
   }
 }
 
@@ -408,35 +442,43 @@ __device__ __forceinline__ void drain_w2(const GemmParams& p, uint32_t taddr, ui
   }
   __nv_bfloat16* dst = base + out_row * p.out_ld + static_cast<long long>(n_tile) * kBlockN;
   const unsigned long long dst_bits = live ? reinterpret_cast<unsigned long long>(dst) : 0ull;
+  // 128 columns per wait: four tensor-memory loads are in flight together (their latency, not
+  // their bandwidth, is what a drain pays for, see drain_w13).
 #pragma unroll 1
-  for (int ch = 0; ch < kBlockN / 64; ++ch) {
+  for (int half = 0; half < kBlockN / 128; ++half) {
+    uint32_t v[4][32];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      uint32_t v[32];
-      tmem_ld_32x32(taddr + ch * 64 + h * 32, v);
-      tmem_ld_wait();
-      uint4* s4 = reinterpret_cast<uint4*>(stage_out + lane * kOutStageRowBytes + h * 64);
+    for (int q = 0; q < 4; ++q) tmem_ld_32x32(taddr + half * 128 + q * 32, v[q]);
+    tmem_ld_wait();
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 o;
-        o.x = pack_bf16(__uint_as_float(v[8 * q + 0]) * w, __uint_as_float(v[8 * q + 1]) * w);
-        o.y = pack_bf16(__uint_as_float(v[8 * q + 2]) * w, __uint_as_float(v[8 * q + 3]) * w);
-        o.z = pack_bf16(__uint_as_float(v[8 * q + 4]) * w, __uint_as_float(v[8 * q + 5]) * w);
-        o.w = pack_bf16(__uint_as_float(v[8 * q + 6]) * w, __uint_as_float(v[8 * q + 7]) * w);
-        s4[q] = o;
+    for (int c = 0; c < 2; ++c) {
+      const int ch = half * 2 + c;  // 64-column chunk of the tile
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint4* s4 = reinterpret_cast<uint4*>(stage_out + lane * kOutStageRowBytes + h * 64);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t* w4 = &v[c * 2 + h][8 * q];
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(w4[0]) * w, __uint_as_float(w4[1]) * w);
+          o.y = pack_bf16(__uint_as_float(w4[2]) * w, __uint_as_float(w4[3]) * w);
+          o.z = pack_bf16(__uint_as_float(w4[4]) * w, __uint_as_float(w4[5]) * w);
+          o.w = pack_bf16(__uint_as_float(w4[6]) * w, __uint_as_float(w4[7]) * w);
+          s4[q] = o;
+        }
       }
-    }
-    __syncwarp();
+      __syncwarp();
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = i * 4 + (lane >> 3), piece = lane & 7;
-      const unsigned long long row_dst = __shfl_sync(0xffffffffu, dst_bits, r);
-      if (row_dst != 0ull) {
-        const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
-        *reinterpret_cast<uint4*>(row_dst + static_cast<unsigned long long>(ch) * 128 + piece * 16) = o;
+      for (int i = 0; i < 8; ++i) {
+        const int r = i * 4 + (lane >> 3), piece = lane & 7;
+        const unsigned long long row_dst = __shfl_sync(0xffffffffu, dst_bits, r);
+        if (row_dst != 0ull) {
+          const uint4 o = *reinterpret_cast<const uint4*>(stage_out + r * kOutStageRowBytes + piece * 16);
+          *reinterpret_cast<uint4*>(row_dst + static_cast<unsigned long long>(ch) * 128 + piece * 16) = o;
+        }
       }
+      __syncwarp();
     }
-    __syncwarp();
   }
 }
 
@@ -671,59 +713,174 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // dealt round-robin to the CTAs; a last round that would keep fewer than half of the CTAs busy is
 // dealt as one-block tiles instead, so that round costs half as much.
 // ================================================================================================
-constexpr int kDualStages = 3;
-constexpr int kDualABytes = 2 * kABytes;                      // 32768: 256 rows x 64 columns
-constexpr int kDualStageBytes = kDualABytes + kBBytes;        // 65536
+#ifndef B200MOE_DUAL_STAGES
+#define B200MOE_DUAL_STAGES 3
+#endif
+constexpr int kDualStages = B200MOE_DUAL_STAGES;
+// K step of this kernel: 64 (three stages of 64 KiB, 128-byte swizzle) or, as a build option, 32
+// (six stages of 32 KiB, rows of 64 bytes with the 64-byte swizzle of TMA and of the
+// shared-memory descriptors).  Measured with the cycle counters of a measurement build at
+// T = 8192: with 64-wide steps the MMA thread waits for operands 13-14 % of its time (40 % with
+// two stages: a stage's loads take about 2400 SM cycles to land); the 32-wide variant, meant to
+// reach further ahead (five K steps of lookahead instead of two), was slower (17-18 % waiting,
+// 82 k instead of 73 k cycles per first-GEMM tile): boxes of 64-byte rows are delivered less
+// efficiently than boxes of 128-byte rows.  Asking L2 for the weight boxes four or eight K steps
+// ahead (cp.async.bulk.prefetch.tensor) did not help either: the one-block kernel lost 15-20 %.
+#ifndef B200MOE_DUAL_BLOCK_K
+#define B200MOE_DUAL_BLOCK_K 64
+#endif
+constexpr int kDualBlockK = B200MOE_DUAL_BLOCK_K;
+static_assert(kDualBlockK == 32 || kDualBlockK == 64, "K step of the two-block kernel");
+constexpr int kDualRowBytes = kDualBlockK * 2;
+constexpr int kDualBlockABytes = kBlockM * kDualRowBytes;     // one M block's rows of one stage
+constexpr int kDualABytes = 2 * kDualBlockABytes;
+constexpr int kDualBBytes = kBlockN * kDualRowBytes;
+constexpr int kDualStageBytes = kDualABytes + kDualBBytes;
+
+// Shared-memory matrix descriptor of a K-major tile in this kernel's stage layout: 8-row groups
+// are 8 * row bytes apart; layout type 2 is the 128-byte swizzle, 4 the 64-byte swizzle.
+__device__ __forceinline__ uint64_t make_dual_desc(uint32_t smem_addr) {
+  const uint32_t lo = (smem_addr & 0x3ffffu) >> 4;
+  const uint32_t hi = ((8u * kDualRowBytes) >> 4) | (1u << 14) | ((kDualRowBytes == 128 ? 2u : 4u) << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
 constexpr int kDualSmemBytes = kDualStages * kDualStageBytes + kOutStageBytes + kSmemAlignSlack;
 // Batch size from which the two-block kernel is chosen, in average M blocks per expert that has
 // any (counted on the device, see two_block_tiles_win).  Measured on B200 at Mixtral shape,
-// interleaved runs: the second GEMM (K = 14336, epilogue negligible) gains 8-10 % at T = 8192 and
-// T = 16384 and loses below about six blocks per expert, where the round-robin deal of tiles that
-// cost one or two units leaves CTAs idle (T = 2048 with skewed routing: -13 %); the first GEMM
-// (K = 4096, so the part of the drain that no longer overlaps the next tile's MMAs weighs more)
-// gains 3-4 % at T = 8192 and T = 16384 and nothing at T = 2048.
+// interleaved runs: the second GEMM (K = 14336, epilogue negligible) gains 5-10 % at T = 4096,
+// 8192 and 16384 and loses below about six blocks per expert, where too few tiles are left to
+// deal evenly (T = 2048 with skewed routing: -15 %); the first GEMM (K = 4096, so the part of the
+// drain that no longer overlaps the next tile's MMAs weighs more) gains 4-5 % at T = 16384 and
+// nothing at T = 4096 and T = 8192, where the one-block kernel also reads less from HBM.
 constexpr int kDualMinBlocksPerExpertW2 = 6;
-constexpr int kDualMinBlocksPerExpertW13 = 12;
+constexpr int kDualMinBlocksPerExpertW13 = 24;
 
-struct DualTile {
+// One piece of work of the two-block kernel: m_count = 2 is two M blocks (m_block, m_block + 1) of
+// one expert against one N tile; m_count = 1 is a single block.
+struct WorkItem {
   int expert;
-  int m_block;   // first 128-row block of the tile
+  int m_block;
   int n_tile;
-  int m_count;   // 2, 1, or 0 (an empty slot of the split last round)
+  int m_count;
 };
 
+// The tile sequence of one launch: tiles are dealt round-robin to the CTAs.  An expert with an odd
+// number of blocks leaves one block over, and there are two ways to deal it:
+//   * slots = false: the odd block is the expert's last unit, a one-block tile per N tile.  Such a
+//     tile takes about 0.64 of a two-block tile's time, so CTAs that receive some run ahead of the
+//     others; CTAs that drift apart stop sharing weight tiles through L2 (the first GEMM then
+//     read 45 % more from HBM than its algorithmic bytes in an ncu capture at T = 4096).
+//   * slots = true: the odd block against TWO consecutive N tiles is one tile (a slot), run one
+//     after the other by the same CTA, so every tile is two units of work and the CTAs stay in
+//     step.  Slots sit in the expert's last group of blocks, right behind the two-block tiles
+//     of the same pair of N tiles, so the weight tiles they read are the ones in flight.
+//     Measured: the extra HBM reads of the first GEMM drop from 45 % to 17 %; the second GEMM,
+//     whose tiles are 3.5 times longer (K = 14336), gets slower (two one-block tiles in a row
+//     are a lump of 1.27 two-block times on one CTA), so it keeps slots = false.
+// Inside an expert the units are cut into groups of at most unit_group (sizes as even as
+// possible); inside a group the order is N tile, then unit (see decode_tile).
 struct DualSeq {
-  const int* blk_off;    // [E + 1] M-block offsets per expert
-  const int* unit_off;   // [E + 1] offsets in two-block units (ceil(blocks / 2) per expert)
+  const int* blk_off;          // [E + 1] M-block offsets per expert
+  const long long* tile_off;   // [E + 1] tile offsets per expert
   int n_tiles, num_experts, unit_group;
-  long long total;       // tiles when every unit is one tile
-  long long cut;         // tiles [cut, total) are dealt as one-block halves
+  bool slots;
+  long long total;             // tiles of the launch
+  long long cut;               // tiles [cut, total) are dealt in halves (one unit each)
 };
 
-// The i-th tile of this CTA; false when the CTA has no more work.
-__device__ __forceinline__ bool dual_tile_at(const DualSeq& q, long long i, DualTile* t) {
-  const long long grid = gridDim.x;
-  const long long mine = static_cast<long long>(blockIdx.x) < q.cut
-                             ? (q.cut - blockIdx.x + grid - 1) / grid : 0;
-  long long tile;
-  int half = -1;
-  if (i < mine) {
-    tile = blockIdx.x + i * grid;
+__host__ __device__ inline long long dual_tiles_of_expert(int blocks, int n_tiles, bool slots) {
+  if (!slots) return static_cast<long long>((blocks + 1) >> 1) * n_tiles;
+  return static_cast<long long>(blocks >> 1) * n_tiles + ((blocks & 1) ? (n_tiles + 1) / 2 : 0);
+}
+
+// Where the last round would keep at most half of the CTAs busy with whole tiles, its tiles are
+// dealt in halves instead: that round then costs one unit instead of two.
+__host__ __device__ inline long long dual_cut(long long total, int grid) {
+  const long long cut = total - total % grid;
+  return 2 * (total - cut) > grid ? total : cut;
+}
+
+// Tile number -> up to two halves (each a one-block item); `joint` says that the halves are the
+// two M blocks of a two-block tile (run together), otherwise they are run one after the other.
+__host__ __device__ inline int dual_decode(const DualSeq& q, long long tile, WorkItem (&half)[2],
+                                           bool* joint) {
+  int e = 0;
+  while (e + 1 < q.num_experts && tile >= q.tile_off[e + 1]) ++e;
+  long long local = tile - q.tile_off[e];
+  const int cnt = q.blk_off[e + 1] - q.blk_off[e];
+  const int odd = cnt & 1;
+  const int full = q.slots ? cnt >> 1 : (cnt + 1) >> 1;  // units dealt per N tile
+  const int groups = (q.unit_group > 0 && full > q.unit_group)
+                         ? (full + q.unit_group - 1) / q.unit_group : 1;
+  const int small = full / groups, big = full % groups;  // `big` groups of small + 1 come first
+  const long long before_last = static_cast<long long>(full - small) * q.n_tiles;
+  int unit = -1, n = 0;
+  if (!odd || !q.slots || local < before_last) {
+    int first, size;
+    const long long big_tiles = static_cast<long long>(small + 1) * q.n_tiles;
+    if (local < big * big_tiles) {
+      const int gi = static_cast<int>(local / big_tiles);
+      first = gi * (small + 1);
+      size = small + 1;
+      local -= gi * big_tiles;
+    } else {
+      local -= big * big_tiles;
+      const int gi = static_cast<int>(local / (static_cast<long long>(small) * q.n_tiles));
+      first = big * (small + 1) + gi * small;
+      size = small;
+      local -= static_cast<long long>(gi) * small * q.n_tiles;
+    }
+    n = static_cast<int>(local / size);
+    unit = first + static_cast<int>(local % size);
   } else {
-    const long long v = blockIdx.x + (i - mine) * grid;
-    if (v >= 2 * (q.total - q.cut)) return false;
-    tile = q.cut + (v >> 1);
-    half = static_cast<int>(v & 1);
+    // The expert's last group (`small` units) with the odd block's slots woven in: per pair of N
+    // tiles, the units against the first, the units against the second, then the slot.
+    local -= before_last;
+    const int size = small, first = full - small;
+    const int pair = static_cast<int>(local / (2 * size + 1));
+    const int r = static_cast<int>(local % (2 * size + 1));
+    const bool last_alone = 2 * pair + 1 >= q.n_tiles;  // odd number of N tiles: a final half pair
+    if (r < size) {
+      n = 2 * pair;
+      unit = first + r;
+    } else if (!last_alone && r < 2 * size) {
+      n = 2 * pair + 1;
+      unit = first + r - size;
+    } else {
+      half[0] = WorkItem{e, q.blk_off[e] + cnt - 1, 2 * pair, 1};
+      half[1] = WorkItem{e, q.blk_off[e] + cnt - 1, 2 * pair + 1, 1};
+      *joint = false;
+      return last_alone ? 1 : 2;
+    }
   }
-  const TileCoord c = decode_tile(tile, q.n_tiles, q.num_experts, q.unit_off, q.unit_group);
-  const int unit = c.m_block - q.unit_off[c.expert];
-  const int cnt = q.blk_off[c.expert + 1] - q.blk_off[c.expert];
-  const int natural = 2 * unit + 1 < cnt ? 2 : 1;
-  t->expert = c.expert;
-  t->n_tile = c.n_tile;
-  t->m_block = q.blk_off[c.expert] + 2 * unit + (half > 0 ? 1 : 0);
-  t->m_count = half < 0 ? natural : (half == 0 ? 1 : natural - 1);
-  return true;
+  half[0] = WorkItem{e, q.blk_off[e] + 2 * unit, n, 1};
+  half[1] = WorkItem{e, q.blk_off[e] + 2 * unit + 1, n, 1};
+  *joint = 2 * unit + 1 < cnt;
+  return *joint ? 2 : 1;  // without slots the odd block is the expert's last, one-block unit
+}
+
+// The work of CTA `cta` of `grid` in its i-th turn: 0, 1 or 2 items, or -1 when it has no more.
+__host__ __device__ inline int dual_items_at(const DualSeq& q, long long i, int cta, int grid,
+                                             WorkItem (&items)[2]) {
+  const long long mine = cta < q.cut ? (q.cut - cta + grid - 1) / grid : 0;
+  WorkItem half[2];
+  bool joint = false;
+  if (i < mine) {
+    const int halves = dual_decode(q, cta + i * grid, half, &joint);
+    if (joint) {
+      items[0] = WorkItem{half[0].expert, half[0].m_block, half[0].n_tile, 2};
+      return 1;
+    }
+    items[0] = half[0];
+    items[1] = half[1];
+    return halves;
+  }
+  const long long v = cta + (i - mine) * grid;
+  if (v >= 2 * (q.total - q.cut)) return -1;
+  const int halves = dual_decode(q, q.cut + (v >> 1), half, &joint);
+  if (static_cast<int>(v & 1) >= halves) return 0;
+  items[0] = half[v & 1];
+  return 1;
 }
 
 template <int kMode>
@@ -737,13 +894,14 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
   __shared__ uint32_t tmem_slot;
   __shared__ int s_blk_cnt[kMaxExperts];
   __shared__ int s_blk_off[kMaxExperts + 1];
-  __shared__ int s_unit_off[kMaxExperts + 1];
+  __shared__ long long s_tile_off[kMaxExperts + 1];
   __shared__ int s_abort;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + kSmemAlignSlack - 1) &
       ~static_cast<uintptr_t>(kSmemAlignSlack - 1));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, grid = gridDim.x;
 
   // ------------------------------------------------------------------ prologue
   if (threadIdx.x == 0) {
@@ -778,15 +936,16 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int acc = 0, units = 0;
+    int acc = 0;
+    long long tiles = 0;
     for (int e = 0; e < p.num_experts; ++e) {
       s_blk_off[e] = acc;
-      s_unit_off[e] = units;
+      s_tile_off[e] = tiles;
       acc += s_blk_cnt[e];
-      units += (s_blk_cnt[e] + 1) >> 1;
+      tiles += dual_tiles_of_expert(s_blk_cnt[e], p.n_tiles, kMode != kW2);
     }
     s_blk_off[p.num_experts] = acc;
-    s_unit_off[p.num_experts] = units;
+    s_tile_off[p.num_experts] = tiles;
   }
   tc_fence_before();
   __syncthreads();
@@ -796,45 +955,51 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
 
   DualSeq seq;
   seq.blk_off = s_blk_off;
-  seq.unit_off = s_unit_off;
+  seq.tile_off = s_tile_off;
   seq.n_tiles = p.n_tiles;
   seq.num_experts = p.num_experts;
   seq.unit_group = p.m_group > 0 ? (p.m_group + 1) / 2 : 0;
-  seq.total = static_cast<long long>(s_unit_off[p.num_experts]) * p.n_tiles;
+  seq.slots = kMode != kW2;
+  seq.total = s_tile_off[p.num_experts];
   if (p.dual_min_blocks > 0 && !two_block_tiles_win(s_blk_off, p.num_experts, p.dual_min_blocks))
     seq.total = 0;  // the one-block kernel launched beside this one does the work
-  seq.cut = seq.total - seq.total % gridDim.x;
-  if (2 * (seq.total - seq.cut) > static_cast<long long>(gridDim.x)) seq.cut = seq.total;
+  seq.cut = dual_cut(seq.total, grid);
 
   constexpr bool kIsW13 = (kMode != kW2);
-  const int b_tx_bytes = p.stage_tx_bytes - kABytes;  // weight bytes of one stage
+  // The host sizes K steps and stage bytes for the 64-wide K step of the other kernels.
+  const int k_blocks = p.k_blocks * (kBlockK / kDualBlockK);
+  const int b_tx_bytes = (p.stage_tx_bytes - kABytes) / (kBlockK / kDualBlockK);  // weight bytes of one stage
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      DualTile t;
-      for (long long i = 0; ok && dual_tile_at(seq, i, &t); ++i) {
-        if (t.m_count == 0) continue;
+      WorkItem items[2];
+      for (long long i = 0; ok; ++i) {
+        const int count = dual_items_at(seq, i, cta, grid, items);
+        if (count < 0) break;
+        for (int s = 0; ok && s < count; ++s) {
+        const WorkItem t = items[s];
         const int a_row = t.m_block * kBlockM;
         const int b_row0 = t.expert * p.b_rows_per_expert +
                            t.n_tile * (kIsW13 ? p.half_n : kBlockN);
-        const uint32_t tx = b_tx_bytes + t.m_count * kABytes;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const uint32_t tx = b_tx_bytes + t.m_count * kDualBlockABytes;
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 0x121)) { ok = false; break; }
           uint8_t* sa = smem + stage * kDualStageBytes;
           uint8_t* sb = sa + kDualABytes;
           mbar_expect_tx(&full_bar[stage], tx);
-          tma_load_2d(sa, t.m_count == 2 ? &tmap_a2 : &tmap_a, &full_bar[stage], kb * kBlockK, a_row);
+          tma_load_2d(sa, t.m_count == 2 ? &tmap_a2 : &tmap_a, &full_bar[stage], kb * kDualBlockK, a_row);
           if (kIsW13) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
-            tma_load_2d(sb + p.half_n * (kBlockK * 2), &tmap_b, &full_bar[stage], kb * kBlockK,
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kDualBlockK, b_row0);
+            tma_load_2d(sb + p.half_n * kDualRowBytes, &tmap_b, &full_bar[stage], kb * kDualBlockK,
                         b_row0 + p.inter);
           } else {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBlockK, b_row0);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kDualBlockK, b_row0);
           }
           if (++stage == kDualStages) { stage = 0; phase ^= 1; }
+        }
         }
       }
     }
@@ -846,54 +1011,72 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
       uint32_t phase = 0;
       bool ok = true;
       long long it = 0;
-      DualTile t;
+      WorkItem items[2];
       const uint32_t acc0 = tmem_base, acc1 = tmem_base + kBlockN;
-      for (long long i = 0; ok && dual_tile_at(seq, i, &t); ++i) {
-        if (t.m_count == 0) continue;
+      long long cyc_full = 0, cyc_tmem = 0, cyc_head = 0, cyc_tail = 0;
+      B200MOE_CYCLES_BEGIN(loop_begin);
+      for (long long i = 0; ok; ++i) {
+        const int count = dual_items_at(seq, i, cta, grid, items);
+        if (count < 0) break;
+        for (int s = 0; ok && s < count; ++s) {
+        const WorkItem t = items[s];
         const uint32_t par = static_cast<uint32_t>(it & 1);
         ++it;
-        if (!mbar_wait(&tmem_empty_bar[0], par ^ 1, abort_flag, 0x221)) { ok = false; break; }
+        {
+          B200MOE_CYCLES_BEGIN(w0);
+          if (!mbar_wait(&tmem_empty_bar[0], par ^ 1, abort_flag, 0x221)) { ok = false; break; }
+          B200MOE_CYCLES_ADD(cyc_tmem, w0);
+        }
         tc_fence_after();
         int kb = 0;
         if (t.m_count == 2) {
           // Block 0 runs ahead over the first K steps while block 1's accumulator is drained.
-          const int head = p.k_blocks < kDualStages ? p.k_blocks : kDualStages;
+          const int head = k_blocks < kDualStages ? k_blocks : kDualStages;
           for (int h = 0; ok && h < head; ++h) {
             const int st = stage + h < kDualStages ? stage + h : stage + h - kDualStages;
             const uint32_t ph = stage + h < kDualStages ? phase : phase ^ 1;
+            B200MOE_CYCLES_BEGIN(w1);
             if (!mbar_wait(&full_bar[st], ph, abort_flag, 0x222)) { ok = false; break; }
+            B200MOE_CYCLES_ADD(cyc_full, w1);
+            B200MOE_CYCLES_ADD(cyc_head, w1);
             const uint32_t sa = smem_u32(smem + st * kDualStageBytes);
             const uint32_t sb = sa + kDualABytes;
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), make_smem_desc(sb + k * kUmmaK * 2),
+            for (int k = 0; k < kDualBlockK / kUmmaK; ++k)
+              umma_bf16(acc0, make_dual_desc(sa + k * kUmmaK * 2), make_dual_desc(sb + k * kUmmaK * 2),
                         p.idesc, (h | k) != 0 ? 1u : 0u);
           }
           if (!ok) break;
-          if (!mbar_wait(&tmem_empty_bar[1], par ^ 1, abort_flag, 0x223)) { ok = false; break; }
+          {
+            B200MOE_CYCLES_BEGIN(w2);
+            if (!mbar_wait(&tmem_empty_bar[1], par ^ 1, abort_flag, 0x223)) { ok = false; break; }
+            B200MOE_CYCLES_ADD(cyc_tmem, w2);
+          }
           tc_fence_after();
           for (int h = 0; h < head; ++h) {
             const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
             const uint32_t sb = sa + kDualABytes;
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              umma_bf16(acc1, make_smem_desc(sa + kABytes + k * kUmmaK * 2),
-                        make_smem_desc(sb + k * kUmmaK * 2), p.idesc, (h | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kDualBlockK / kUmmaK; ++k)
+              umma_bf16(acc1, make_dual_desc(sa + kDualBlockABytes + k * kUmmaK * 2),
+                        make_dual_desc(sb + k * kUmmaK * 2), p.idesc, (h | k) != 0 ? 1u : 0u);
             umma_commit(&empty_bar[stage]);
             if (++stage == kDualStages) { stage = 0; phase ^= 1; }
           }
           // The last K steps mirror the first: block 0 finishes them first and is handed to the
           // epilogue while block 1 runs them.
-          const int tail = p.k_blocks - head >= kDualStages ? kDualStages : 0;
-          for (kb = head; kb < p.k_blocks - tail; ++kb) {
+          const int tail = k_blocks - head >= kDualStages ? kDualStages : 0;
+          for (kb = head; kb < k_blocks - tail; ++kb) {
+            B200MOE_CYCLES_BEGIN(w3);
             if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x224)) { ok = false; break; }
+            B200MOE_CYCLES_ADD(cyc_full, w3);
             const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
             const uint32_t sb = sa + kDualABytes;
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-              const uint64_t bdesc = make_smem_desc(sb + k * kUmmaK * 2);
-              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), bdesc, p.idesc, 1u);
-              umma_bf16(acc1, make_smem_desc(sa + kABytes + k * kUmmaK * 2), bdesc, p.idesc, 1u);
+            for (int k = 0; k < kDualBlockK / kUmmaK; ++k) {
+              const uint64_t bdesc = make_dual_desc(sb + k * kUmmaK * 2);
+              umma_bf16(acc0, make_dual_desc(sa + k * kUmmaK * 2), bdesc, p.idesc, 1u);
+              umma_bf16(acc1, make_dual_desc(sa + kDualBlockABytes + k * kUmmaK * 2), bdesc, p.idesc, 1u);
             }
             umma_commit(&empty_bar[stage]);
             if (++stage == kDualStages) { stage = 0; phase ^= 1; }
@@ -902,12 +1085,15 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
           for (int h = 0; ok && h < tail; ++h) {
             const int st = stage + h < kDualStages ? stage + h : stage + h - kDualStages;
             const uint32_t ph = stage + h < kDualStages ? phase : phase ^ 1;
+            B200MOE_CYCLES_BEGIN(w4);
             if (!mbar_wait(&full_bar[st], ph, abort_flag, 0x227)) { ok = false; break; }
+            B200MOE_CYCLES_ADD(cyc_full, w4);
+            B200MOE_CYCLES_ADD(cyc_tail, w4);
             const uint32_t sa = smem_u32(smem + st * kDualStageBytes);
             const uint32_t sb = sa + kDualABytes;
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), make_smem_desc(sb + k * kUmmaK * 2),
+            for (int k = 0; k < kDualBlockK / kUmmaK; ++k)
+              umma_bf16(acc0, make_dual_desc(sa + k * kUmmaK * 2), make_dual_desc(sb + k * kUmmaK * 2),
                         p.idesc, 1u);
           }
           if (!ok) break;
@@ -916,9 +1102,9 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
             const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
             const uint32_t sb = sa + kDualABytes;
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              umma_bf16(acc1, make_smem_desc(sa + kABytes + k * kUmmaK * 2),
-                        make_smem_desc(sb + k * kUmmaK * 2), p.idesc, 1u);
+            for (int k = 0; k < kDualBlockK / kUmmaK; ++k)
+              umma_bf16(acc1, make_dual_desc(sa + kDualBlockABytes + k * kUmmaK * 2),
+                        make_dual_desc(sb + k * kUmmaK * 2), p.idesc, 1u);
             umma_commit(&empty_bar[stage]);
             if (++stage == kDualStages) { stage = 0; phase ^= 1; }
           }
@@ -926,13 +1112,15 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
         } else {
           if (!mbar_wait(&tmem_empty_bar[1], par ^ 1, abort_flag, 0x225)) { ok = false; break; }
           tc_fence_after();
-          for (kb = 0; kb < p.k_blocks; ++kb) {
+          for (kb = 0; kb < k_blocks; ++kb) {
+            B200MOE_CYCLES_BEGIN(w5);
             if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x226)) { ok = false; break; }
+            B200MOE_CYCLES_ADD(cyc_full, w5);
             const uint32_t sa = smem_u32(smem + stage * kDualStageBytes);
             const uint32_t sb = sa + kDualABytes;
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              umma_bf16(acc0, make_smem_desc(sa + k * kUmmaK * 2), make_smem_desc(sb + k * kUmmaK * 2),
+            for (int k = 0; k < kDualBlockK / kUmmaK; ++k)
+              umma_bf16(acc0, make_dual_desc(sa + k * kUmmaK * 2), make_dual_desc(sb + k * kUmmaK * 2),
                         p.idesc, (kb | k) != 0 ? 1u : 0u);
             umma_commit(&empty_bar[stage]);
             if (++stage == kDualStages) { stage = 0; phase ^= 1; }
@@ -942,7 +1130,20 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
             umma_commit(&tmem_full_bar[1]);  // keeps the two barriers in step; nothing to drain
           }
         }
+        }
       }
+#ifdef B200MOE_MEASURE_CYCLES
+      atomicAdd(&g_gemm_cycles[2], static_cast<unsigned long long>(cyc_full));
+      atomicAdd(&g_gemm_cycles[3], static_cast<unsigned long long>(cyc_tmem));
+      atomicAdd(&g_gemm_cycles[4], static_cast<unsigned long long>(clock64() - loop_begin));
+      atomicAdd(&g_gemm_cycles[5], static_cast<unsigned long long>(it));
+      atomicAdd(&g_gemm_cycles[6], static_cast<unsigned long long>(cyc_head));
+      atomicAdd(&g_gemm_cycles[7], static_cast<unsigned long long>(cyc_tail));
+#endif
+      (void)cyc_full;
+      (void)cyc_tmem;
+      (void)cyc_head;
+      (void)cyc_tail;
     }
     __syncwarp();
   } else {
@@ -951,10 +1152,13 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
     uint8_t* stage_out = smem + kDualStages * kDualStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
-    long long it = 0;
-    DualTile t;
-    for (long long i = 0; ok && dual_tile_at(seq, i, &t); ++i) {
-      if (t.m_count == 0) continue;
+    long long it = 0, cyc_drain = 0, drains = 0;
+    WorkItem items[2];
+    for (long long i = 0; ok; ++i) {
+      const int count = dual_items_at(seq, i, cta, grid, items);
+      if (count < 0) break;
+      for (int s = 0; ok && s < count; ++s) {
+      const WorkItem t = items[s];
       const uint32_t par = static_cast<uint32_t>(it & 1);
       ++it;
       for (int b = 0; b < 2; ++b) {
@@ -964,18 +1168,30 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
         if (!good) { ok = false; break; }
         tc_fence_after();
         if (b < t.m_count) {
+          B200MOE_CYCLES_BEGIN(d0);
           if (kIsW13) {
             drain_w13(p, taddr + b * kBlockN, stage_out, t.m_block + b, t.n_tile, quarter, lane);
           } else {
             drain_w2(p, taddr + b * kBlockN, stage_out, t.m_block + b, t.n_tile, quarter, lane);
           }
+          B200MOE_CYCLES_ADD(cyc_drain, d0);
+          ++drains;
         }
         // Hand this accumulator back to the MMA warp.
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty_bar[b]);
       }
+      }
     }
+#ifdef B200MOE_MEASURE_CYCLES
+    if (warp == 2 && lane == 0) {
+      atomicAdd(&g_gemm_cycles[0], static_cast<unsigned long long>(cyc_drain));
+      atomicAdd(&g_gemm_cycles[1], static_cast<unsigned long long>(drains));
+    }
+#endif
+    (void)cyc_drain;
+    (void)drains;
   }
 
   // ------------------------------------------------------------------ teardown
@@ -1314,18 +1530,20 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor [rows, cols] (cols contiguous), box = box_rows x 64 columns, 128-byte swizzle.
+// 2-D bf16 tensor [rows, cols] (cols contiguous), box = box_rows x box_cols columns; rows of 64
+// columns take the 128-byte swizzle, rows of 32 the 64-byte swizzle.
 int make_tmap(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows,
-              const char* what) {
+              const char* what, int box_cols = kBlockK) {
   auto encode = get_encode_fn();
   if (!encode) return fail(B200MOE_ERR_CUDA, "%s: cuTensorMapEncodeTiled is unavailable", what);
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            box_cols == kBlockK ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(B200MOE_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
@@ -1378,14 +1596,27 @@ TileChoice choose_tiles(int64_t capacity, int num_experts, int min_blocks_per_ex
   return pairs >= static_cast<int64_t>(kBlockM) * min_blocks_per_expert ? kDecideOnDevice : kOneBlock;
 }
 
+// Tensor maps of the two-block kernel (its own K step and swizzle): A rows in boxes of one and of
+// two M blocks, and the weight rows.
+struct DualMaps {
+  CUtensorMap a, a2, b;
+};
+
+int make_dual_maps(DualMaps* m, const void* a, long long a_rows, long long k, const void* b,
+                   long long b_rows, int b_box_rows, const char* what) {
+  if (int rc = make_tmap(&m->a, a, a_rows, k, kBlockM, what, kDualBlockK)) return rc;
+  if (int rc = make_tmap(&m->a2, a, a_rows, k, 2 * kBlockM, what, kDualBlockK)) return rc;
+  return make_tmap(&m->b, b, b_rows, k, b_box_rows, what, kDualBlockK);
+}
+
 template <int kMode>
-int launch_chosen(TileChoice choice, int min_blocks, const CUtensorMap& ta, const CUtensorMap& ta2,
-                  const CUtensorMap& tb, GemmParams p, cudaStream_t st) {
+int launch_chosen(TileChoice choice, int min_blocks, const CUtensorMap& ta, const CUtensorMap& tb,
+                  const DualMaps& dm, GemmParams p, cudaStream_t st) {
   if (choice == kOneBlock) return launch<kMode>(ta, tb, p, st);
-  if (choice == kTwoBlock) return launch_dual<kMode>(ta, ta2, tb, p, st);
+  if (choice == kTwoBlock) return launch_dual<kMode>(dm.a, dm.a2, dm.b, p, st);
   p.dual_min_blocks = min_blocks;
   if (int rc = launch<kMode>(ta, tb, p, st)) return rc;
-  return launch_dual<kMode>(ta, ta2, tb, p, st);
+  return launch_dual<kMode>(dm.a, dm.a2, dm.b, p, st);
 }
 
 template <int kMode>
@@ -1484,13 +1715,16 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   const bool two_block = tiles != kOneBlock;
   const int half_n = block_m == kPairBlockM ? kBlockN / 2
                                             : choose_half_n(sorted_capacity, num_experts, inter);
-  CUtensorMap ta, ta2, tb;
+  CUtensorMap ta, tb;
+  DualMaps dm;
   if (int rc = make_tmap(&ta, a_sorted, sorted_capacity, hidden, kBlockM, name)) return rc;
-  if (two_block)
-    if (int rc = make_tmap(&ta2, a_sorted, sorted_capacity, hidden, 2 * kBlockM, name)) return rc;
   if (int rc = make_tmap(&tb, w13, static_cast<long long>(num_experts) * 2 * inter, hidden, half_n,
                          name))
     return rc;
+  if (two_block)
+    if (int rc = make_dual_maps(&dm, a_sorted, sorted_capacity, hidden, w13,
+                                static_cast<long long>(num_experts) * 2 * inter, half_n, name))
+      return rc;
   GemmParams p{};
   p.expert_ids = expert_ids;
   p.npp = num_tokens_post_pad;
@@ -1506,7 +1740,7 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   set_width(&p, 2 * half_n);
   p.m_group = m_group_for(hidden * 2);
   if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW13>(tiles, kDualMinBlocksPerExpertW13, ta, ta2, tb, p,
+  return launch_chosen<kW13>(tiles, kDualMinBlocksPerExpertW13, ta, tb, dm, p,
                              static_cast<cudaStream_t>(stream));
 }
 
@@ -1585,10 +1819,13 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
                                ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2)
                                : kOneBlock;
   const bool two_block = tiles != kOneBlock;
-  CUtensorMap ta, ta2, tb;
+  CUtensorMap ta, tb;
+  DualMaps dm;
   if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
   if (two_block)
-    if (int rc = make_tmap(&ta2, act, sorted_capacity, inter, 2 * kBlockM, name)) return rc;
+    if (int rc = make_dual_maps(&dm, act, sorted_capacity, inter, w2,
+                                static_cast<long long>(num_experts) * hidden, kBlockN, name))
+      return rc;
   // The two-CTA kernel fetches the B tile as two boxes of 128 rows, one per CTA.
   if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter,
                          block_m == kPairBlockM ? kBlockN / 2 : kBlockN, name))
@@ -1610,7 +1847,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, ta2, tb, p,
+  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, tb, dm, p,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -1640,10 +1877,13 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
                                ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2)
                                : kOneBlock;
   const bool two_block = tiles != kOneBlock;
-  CUtensorMap ta, ta2, tb;
+  CUtensorMap ta, tb;
+  DualMaps dm;
   if (int rc = make_tmap(&ta, act, sorted_capacity, inter, kBlockM, name)) return rc;
   if (two_block)
-    if (int rc = make_tmap(&ta2, act, sorted_capacity, inter, 2 * kBlockM, name)) return rc;
+    if (int rc = make_dual_maps(&dm, act, sorted_capacity, inter, w2,
+                                static_cast<long long>(num_experts) * hidden, kBlockN, name))
+      return rc;
   if (int rc = make_tmap(&tb, w2, static_cast<long long>(num_experts) * hidden, inter,
                          block_m == kPairBlockM ? kBlockN / 2 : kBlockN, name))
     return rc;
@@ -1666,8 +1906,52 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, ta2, tb, p,
+  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, tb, dm, p,
                             static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t b200moe_gemm_two_block_schedule(const int32_t* blocks_per_expert, int num_experts,
+                                                   int n_tiles, int m_group, int slots, int grid,
+                                                   int cta, int32_t* items, int64_t max_items) {
+  using namespace b200moe;
+  if (!blocks_per_expert || num_experts < 1 || num_experts > kMaxExperts || n_tiles < 1 ||
+      grid < 1 || cta < 0 || cta >= grid || max_items < 0 || (max_items > 0 && !items))
+    return fail(B200MOE_ERR_SHAPE, "gemm_two_block_schedule: bad arguments");
+  int blk_off[kMaxExperts + 1];
+  long long tile_off[kMaxExperts + 1];
+  blk_off[0] = 0;
+  tile_off[0] = 0;
+  for (int e = 0; e < num_experts; ++e) {
+    if (blocks_per_expert[e] < 0)
+      return fail(B200MOE_ERR_SHAPE, "gemm_two_block_schedule: negative block count");
+    blk_off[e + 1] = blk_off[e] + blocks_per_expert[e];
+    tile_off[e + 1] = tile_off[e] + dual_tiles_of_expert(blocks_per_expert[e], n_tiles, slots != 0);
+  }
+  DualSeq seq;
+  seq.blk_off = blk_off;
+  seq.tile_off = tile_off;
+  seq.n_tiles = n_tiles;
+  seq.num_experts = num_experts;
+  seq.unit_group = m_group > 0 ? (m_group + 1) / 2 : 0;
+  seq.slots = slots != 0;
+  seq.total = tile_off[num_experts];
+  seq.cut = dual_cut(seq.total, grid);
+  int64_t written = 0;
+  WorkItem w[2];
+  for (long long i = 0;; ++i) {
+    const int count = dual_items_at(seq, i, cta, grid, w);
+    if (count < 0) break;
+    for (int s = 0; s < count; ++s) {
+      if (written < max_items) {
+        items[4 * written + 0] = w[s].expert;
+        items[4 * written + 1] = w[s].m_block;
+        items[4 * written + 2] = w[s].n_tile;
+        items[4 * written + 3] = w[s].m_count;
+      }
+      ++written;
+    }
+  }
+  return written;
 }
 
 extern "C" int b200moe_gemm_set_tiling(int mode) {
@@ -1676,6 +1960,26 @@ extern "C" int b200moe_gemm_set_tiling(int mode) {
     return fail(B200MOE_ERR_SHAPE, "gemm_set_tiling: mode must be 0 (automatic), 1 or 2, got %d", mode);
   g_tiling.store(mode, std::memory_order_relaxed);
   return B200MOE_OK;
+}
+
+extern "C" int b200moe_gemm_measured_cycles(uint64_t* out8, int reset) {
+  using namespace b200moe;
+  uint64_t* out6 = out8;
+  if (!out6) return fail(B200MOE_ERR_NULL, "gemm_measured_cycles: null pointer");
+  unsigned long long v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(v, g_gemm_cycles, sizeof(v));
+  if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "gemm_measured_cycles: %s", cudaGetErrorString(e));
+  for (int i = 0; i < 8; ++i) out6[i] = v[i];
+  if (reset) {
+    const unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_gemm_cycles, zero, sizeof(zero));
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "gemm_measured_cycles: %s", cudaGetErrorString(e));
+  }
+#ifdef B200MOE_MEASURE_CYCLES
+  return 1;
+#else
+  return 0;
+#endif
 }
 
 extern "C" int b200moe_gemm_device_status(int reset) {

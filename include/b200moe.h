@@ -394,15 +394,44 @@ int b200moe_paged_attn_varlen(const void* q, const void* k_cache, const void* v_
 int b200moe_gemm_device_status(int reset);
 
 /*
+ * Cycle accounting of the two-block grouped GEMM, for measurement builds of the library
+ * (csrc/grouped_gemm.cu compiled with -DB200MOE_MEASURE_CYCLES; the shipped build records
+ * nothing).  Fills out8 with sums over all CTAs since the last reset: [0] SM cycles one epilogue
+ * warp spent draining accumulators, [1] accumulators it drained, [2] cycles the MMA-issuing thread
+ * waited for operand stages, [3] cycles it waited for a free accumulator, [4] cycles it spent in
+ * its tile loop, [5] tiles it processed, [6] and [7] the part of [2] that fell into the first and
+ * the last K steps of two-block tiles (where block 0 runs ahead of block 1).  Synchronises with the device.  Returns 1 for a
+ * measurement build, 0 for a normal build (all zeros), or a negative B200MOE_ERR_*.
+ */
+int b200moe_gemm_measured_cycles(uint64_t* out8, int reset);
+
+/*
  * Tiling of the one-CTA grouped GEMMs (block_m = 128), a process-wide setting for benchmarks and
  * tests: 0 (default) chooses by batch size, 1 forces one 128-row M block per tile (128 x 256
  * accumulator, double-buffered in tensor memory), 2 forces two M blocks of one expert per tile
  * (they share every weight stage; chosen by default, on the device from the real block counts,
- * for the second GEMM from about six M blocks per expert on and for the first from about twelve).
+ * for the second GEMM from about six M blocks per expert on and for the first from about
+ * twenty-four).
  * All tilings produce the same bits.  The reference's counterpart is the tile configuration table
  * of layers/moe/fused_moe.py:327-339.  Returns 0 or B200MOE_ERR_SHAPE.
  */
 int b200moe_gemm_set_tiling(int mode);
+
+/*
+ * Host-side view of the work list of the two-block tiling, for tests and tuning: the items that
+ * CTA `cta` of `grid` processes, in order, when the experts hold `blocks_per_expert[e]` M blocks
+ * of 128 rows, the output has `n_tiles` N tiles, `m_group` is the L2 grouping of M blocks and
+ * `slots` says how the odd block of an expert is dealt (non-zero, the first GEMM: against two N
+ * tiles in a row on one CTA; zero, the second GEMM: as a one-block tile per N tile).
+ * Runs the same code as the kernel's scheduler, on the host; no device is touched.  Writes up to
+ * `max_items` quadruples (expert, first M block, N tile, M blocks in the item: 1 or 2) to `items`
+ * and returns the number of items of that CTA (which may exceed `max_items`), or a negative
+ * B200MOE_ERR_*.  No counterpart in the reference (its launch grid is one program per tile,
+ * layers/moe/fused_moe.py:296-325).
+ */
+int64_t b200moe_gemm_two_block_schedule(const int32_t* blocks_per_expert, int num_experts,
+                                        int n_tiles, int m_group, int slots, int grid, int cta,
+                                        int32_t* items, int64_t max_items);
 
 #ifdef __cplusplus
 }
