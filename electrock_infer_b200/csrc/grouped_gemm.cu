@@ -745,15 +745,22 @@ __device__ __forceinline__ uint64_t make_dual_desc(uint32_t smem_addr) {
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 constexpr int kDualSmemBytes = kDualStages * kDualStageBytes + kOutStageBytes + kSmemAlignSlack;
-// Batch size from which the two-block kernel is chosen, in average M blocks per expert that has
-// any (counted on the device, see two_block_tiles_win).  Measured on B200 at Mixtral shape,
-// interleaved runs: the second GEMM (K = 14336, epilogue negligible) gains 5-10 % at T = 4096,
-// 8192 and 16384 and loses below about six blocks per expert, where too few tiles are left to
-// deal evenly (T = 2048 with skewed routing: -15 %); the first GEMM (K = 4096, so the part of the
-// drain that no longer overlaps the next tile's MMAs weighs more) gains 4-5 % at T = 16384 and
-// nothing at T = 4096 and T = 8192, where the one-block kernel also reads less from HBM.
-constexpr int kDualMinBlocksPerExpertW2 = 6;
-constexpr int kDualMinBlocksPerExpertW13 = 24;
+// When the two-block kernel is chosen: from an average number of M blocks per expert that has any
+// (counted on the device, see two_block_tiles_win) which depends on the length of the K loop,
+// because the part of the drain that no longer overlaps the next tile's MMAs is paid once per
+// tile.  Measured on B200 at Mixtral shape, interleaved runs: with K = 14336 (second GEMM, 224 K
+// steps) it gains 5-10 % at T = 4096, 8192 and 16384 and loses below about six blocks per expert,
+// where too few tiles are left to deal evenly (T = 2048 with skewed routing: -15 %); with
+// K = 4096 (first GEMM, 64 K steps) it gains 4-5 % at T = 16384 and nothing at T = 4096 and
+// T = 8192, where the one-block kernel also reads less from HBM.  Shorter K loops (the second
+// GEMM of a tensor-parallel shard of eight has 28 K steps) keep the one-block kernel.
+constexpr int kDualLongK = 96, kDualShortK = 48;       // in K steps of 64
+constexpr int kDualMinBlocksLongK = 6, kDualMinBlocksMidK = 24;
+
+// 0: never.
+inline int dual_min_blocks_for(int k_blocks) {
+  return k_blocks >= kDualLongK ? kDualMinBlocksLongK : (k_blocks >= kDualShortK ? kDualMinBlocksMidK : 0);
+}
 
 // One piece of work of the two-block kernel: m_count = 2 is two M blocks (m_block, m_block + 1) of
 // one expert against one N tile; m_count = 1 is a single block.
@@ -1592,6 +1599,7 @@ TileChoice choose_tiles(int64_t capacity, int num_experts, int min_blocks_per_ex
   const int mode = g_tiling.load(std::memory_order_relaxed);
   if (capacity < 2 * kBlockM || mode == 1) return kOneBlock;
   if (mode == 2) return kTwoBlock;
+  if (min_blocks_per_expert <= 0) return kOneBlock;
   const int64_t pairs = capacity - static_cast<int64_t>(num_experts) * (kBlockM - 1);
   return pairs >= static_cast<int64_t>(kBlockM) * min_blocks_per_expert ? kDecideOnDevice : kOneBlock;
 }
@@ -1709,9 +1717,9 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   if (!aligned_to(a_sorted, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
   // The two-CTA kernel has a fixed 128 + 128 column tile; the one-CTA kernels pick their width.
-  const TileChoice tiles = block_m == kBlockM
-                               ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW13)
-                               : kOneBlock;
+  const int dual_min_blocks = dual_min_blocks_for(static_cast<int>(hidden / kBlockK));
+  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_min_blocks)
+                                              : kOneBlock;
   const bool two_block = tiles != kOneBlock;
   const int half_n = block_m == kPairBlockM ? kBlockN / 2
                                             : choose_half_n(sorted_capacity, num_experts, inter);
@@ -1740,8 +1748,7 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   set_width(&p, 2 * half_n);
   p.m_group = m_group_for(hidden * 2);
   if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW13>(tiles, kDualMinBlocksPerExpertW13, ta, tb, dm, p,
-                             static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW13>(tiles, dual_min_blocks, ta, tb, dm, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w13_swiglu_gather(
@@ -1815,9 +1822,9 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16) || !aligned_to(out, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  const TileChoice tiles = block_m == kBlockM
-                               ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2)
-                               : kOneBlock;
+  const int dual_min_blocks = dual_min_blocks_for(static_cast<int>(inter / kBlockK));
+  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_min_blocks)
+                                              : kOneBlock;
   const bool two_block = tiles != kOneBlock;
   CUtensorMap ta, tb;
   DualMaps dm;
@@ -1847,8 +1854,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, tb, dm, p,
-                            static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, dm, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w2_scale_peer(
@@ -1873,9 +1879,9 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  const TileChoice tiles = block_m == kBlockM
-                               ? choose_tiles(sorted_capacity, num_experts, kDualMinBlocksPerExpertW2)
-                               : kOneBlock;
+  const int dual_min_blocks = dual_min_blocks_for(static_cast<int>(inter / kBlockK));
+  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_min_blocks)
+                                              : kOneBlock;
   const bool two_block = tiles != kOneBlock;
   CUtensorMap ta, tb;
   DualMaps dm;
@@ -1906,8 +1912,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, kDualMinBlocksPerExpertW2, ta, tb, dm, p,
-                            static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, dm, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t b200moe_gemm_two_block_schedule(const int32_t* blocks_per_expert, int num_experts,

@@ -409,9 +409,9 @@ int b200moe_gemm_measured_cycles(uint64_t* out8, int reset);
  * Tiling of the one-CTA grouped GEMMs (block_m = 128), a process-wide setting for benchmarks and
  * tests: 0 (default) chooses by batch size, 1 forces one 128-row M block per tile (128 x 256
  * accumulator, double-buffered in tensor memory), 2 forces two M blocks of one expert per tile
- * (they share every weight stage; chosen by default, on the device from the real block counts,
- * for the second GEMM from about six M blocks per expert on and for the first from about
- * twenty-four).
+ * (they share every weight stage; chosen by default, on the device from the real block counts:
+ * from about six M blocks per expert on when K is at least 6144, from about twenty-four when K is
+ * at least 3072, never for shorter K).
  * All tilings produce the same bits.  The reference's counterpart is the tile configuration table
  * of layers/moe/fused_moe.py:327-339.  Returns 0 or B200MOE_ERR_SHAPE.
  */
