@@ -680,14 +680,18 @@ extern "C" int b200moe_align_block_size_noalloc(const void* topk_ids, int ids_dt
                 "align_block_size_noalloc: numel=%lld exceeds the built-in scratch limit of %lld "
                 "pair indices; use b200moe_align_block_size with a workspace",
                 (long long)numel, (long long)kStaticMaxIds);
+  // Inputs short enough for the one-launch kernels use no scratch at all: no address look-up then,
+  // so such a call does nothing but launch (also as the first call on a device, or under capture).
   int32_t* scratch = nullptr;
-  if (int rc = static_scratch(&scratch)) return rc;
+  if (numel > kClusterPassMax)
+    if (int rc = static_scratch(&scratch)) return rc;
   // Same validation and the same kernels as the workspace variant; only the scratch differs.
   return b200moe_align_block_size(topk_ids, ids_dtype, numel, num_experts, block_size,
                                   sorted_token_ids, sorted_capacity, expert_ids,
                                   expert_ids_capacity, num_tokens_post_pad, expert_offsets,
                                   fill_pads, scratch,
-                                  static_cast<size_t>(kStaticScratchInts) * sizeof(int32_t), stream);
+                                  scratch ? static_cast<size_t>(kStaticScratchInts) * sizeof(int32_t) : 0,
+                                  stream);
 }
 
 extern "C" size_t b200moe_align_workspace_bytes(int64_t numel, int num_experts) {

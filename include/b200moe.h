@@ -144,8 +144,11 @@ int b200moe_align_max_experts(void);
  * Limits and rules:
  *   - numel <= b200moe_align_noalloc_max_numel() (16 Mi pair indices); larger inputs are rejected
  *     with B200MOE_ERR_SHAPE and must use the workspace variant.
- *   - The first call on each device looks up the device address of the built-in array (a runtime
- *     query, no allocation).  Make that first call during set-up, before any stream capture.
+ *   - The first call on each device with more than b200moe_align_single_pass_max() indices looks up
+ *     the device address of the built-in array (a runtime query, no allocation) and keeps it for
+ *     the life of the process.  Make that first call during set-up, before any stream capture.
+ *     Shorter inputs never touch the array.  The kept address does not survive cudaDeviceReset():
+ *     a process that resets a device must not call this entry point on it afterwards.
  *   - All calls on a device share the one array.  Nothing in it has to be zero beforehand (every
  *     word a call reads is first written by that call), but two calls whose kernels overlap on the
  *     GPU - different streams without ordering between them - race on it and corrupt each other.

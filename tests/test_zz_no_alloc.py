@@ -30,11 +30,15 @@ def _outputs(numel, bs, E=8):
             torch.full((E + 1,), -3, dtype=torch.int32, device=DEV))
 
 
+def _tag(ids):
+    return {torch.int32: _lib.I32, torch.int64: _lib.I64}[ids.dtype]
+
+
 def _with_workspace(lib, ids, bs, fill, stream):
     s, e, n, off = _outputs(ids.numel(), bs)
     ws_bytes = lib.b200moe_align_workspace_bytes(ids.numel(), 8)
     ws = torch.empty(max(ws_bytes // 4, 1), dtype=torch.int32, device=DEV)
-    rc = lib.b200moe_align_block_size(ids.data_ptr(), _lib.I32, ids.numel(), 8, bs, s.data_ptr(),
+    rc = lib.b200moe_align_block_size(ids.data_ptr(), _tag(ids), ids.numel(), 8, bs, s.data_ptr(),
                                       s.numel(), e.data_ptr(), e.numel(), n.data_ptr(),
                                       off.data_ptr(), fill, ws.data_ptr(), ws_bytes, stream)
     _lib.check(rc, "align_block_size")
@@ -44,7 +48,7 @@ def _with_workspace(lib, ids, bs, fill, stream):
 
 def _no_alloc(lib, ids, bs, fill, stream):
     s, e, n, off = _outputs(ids.numel(), bs)
-    rc = lib.b200moe_align_block_size_noalloc(ids.data_ptr(), _lib.I32, ids.numel(), 8, bs,
+    rc = lib.b200moe_align_block_size_noalloc(ids.data_ptr(), _tag(ids), ids.numel(), 8, bs,
                                               s.data_ptr(), s.numel(), e.data_ptr(), e.numel(),
                                               n.data_ptr(), off.data_ptr(), fill, stream)
     _lib.check(rc, "align_block_size_noalloc")
@@ -68,6 +72,10 @@ def test_no_alloc_alignment_matches_workspace_variant_twice_in_a_row():
         got = _no_alloc(lib, ids, bs, fill, stream)
         for a, b in zip(got, want):
             assert torch.equal(a, b)  # integer outputs: bit-exact, untouched slots included
+    # int64 expert ids (what torch.topk hands out) go through the same scratch.
+    wide = second.to(torch.int64)
+    for a, b in zip(_no_alloc(lib, wide, 128, 1, stream), _with_workspace(lib, wide, 128, 1, stream)):
+        assert torch.equal(a, b)
     # Short inputs take the one-launch path and must agree as well.
     short = first[:5000].contiguous()
     for a, b in zip(_no_alloc(lib, short, 128, 1, stream), _with_workspace(lib, short, 128, 1, stream)):
