@@ -725,7 +725,8 @@ constexpr int kDualStages = B200MOE_DUAL_STAGES;
 // reach further ahead (five K steps of lookahead instead of two), was slower (17-18 % waiting,
 // 82 k instead of 73 k cycles per first-GEMM tile): boxes of 64-byte rows are delivered less
 // efficiently than boxes of 128-byte rows.  Asking L2 for the weight boxes four or eight K steps
-// ahead (cp.async.bulk.prefetch.tensor) did not help either: the one-block kernel lost 15-20 %.
+// ahead (cp.async.bulk.prefetch.tensor) did not help either: issued by every CTA the one-block
+// kernel lost 15-20 %, issued only by the one CTA that leads a weight tile it lost 0-8 %.
 #ifndef B200MOE_DUAL_BLOCK_K
 #define B200MOE_DUAL_BLOCK_K 64
 #endif
