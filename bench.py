@@ -51,9 +51,11 @@ from electrock_infer_b200.synthetic import WORKLOADS, MoEWorkload, make_inputs  
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 # DRAM traffic (ncu: dram__bytes_read.sum + dram__bytes_write.sum) over algorithmic bytes, per
-# grouped-GEMM kernel, from one captured launch of each at T=4096.  Traffic is weights + rows x
-# (K + N) x 2 bytes, so a full-size launch is scaled by the same ratio.
-NCU_TRAFFIC_RATIO = {"grouped_gemm_w13_swiglu": 1.006, "grouped_gemm_w2_scale": 1.09}
+# grouped-GEMM kernel, from one captured launch of each at T=4096 with the tilings the benchmark
+# workload runs (first GEMM: one M block per tile, 2.203 / 2.200 GB; second GEMM: two M blocks per
+# tile, 1.997 / 1.256 GB: its weights are streamed once per L2-sized group of A rows by design).
+# Traffic is weights + rows x (K + N) x 2 bytes, so a full-size launch is scaled by the same ratio.
+NCU_TRAFFIC_RATIO = {"grouped_gemm_w13_swiglu": 1.001, "grouped_gemm_w2_scale": 1.59}
 NCU_TRAFFIC_NOTE = ("algorithmic bytes x the ncu DRAM read+write / algorithmic ratio of a captured "
                     "launch of the same kernel at a smaller T")
 PARITY_TOKENS = 64
