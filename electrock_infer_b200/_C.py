@@ -164,6 +164,11 @@ def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: i
         ws.record_stream(torch.cuda.current_stream(dev))
 
 
+def align_single_pass_max() -> int:
+    """Longest input (pair indices) that ``moe_align_block_size`` handles in one launch."""
+    return _lib.load().b200moe_align_single_pass_max()
+
+
 def align_workspace_numel(numel: int, num_experts: int) -> int:
     """int32 elements of scratch that ``moe_align_block_size`` needs for ``numel`` pair indices
     (0 for short inputs)."""

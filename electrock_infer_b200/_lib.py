@@ -70,6 +70,11 @@ SIGNATURES = {
     "b200moe_peer_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "b200moe_peer_close": (c_int, [c_void_p]),
     "b200moe_peer_free": (c_int, [c_void_p]),
+    "b200moe_fused_experts_rows": (c_size_t, [c_int64, c_int, c_int]),
+    "b200moe_fused_experts": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
+                                      c_void_p, c_void_p, c_void_p]),
     "b200moe_gemm_device_status": (c_int, [c_int]),
     "b200moe_gemm_measured_cycles": (c_int, [c_void_p, c_int]),
     "b200moe_gemm_set_tiling": (c_int, [c_int]),

@@ -145,6 +145,7 @@ class _Workspace:
 
 
 _workspace = _Workspace()
+_LOGIT_TAGS = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 
 
 def reserve_workspace(device, max_tokens: int, topk: int, num_experts: int, hidden: int,
@@ -290,6 +291,25 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
     gating = None
     if gate_weight is None:
         gating = gating_output if gating_output.is_contiguous() else gating_output.contiguous()
+
+    if (gate_weight is None and tp_reduce is None and not _timing_enabled and block_m == BLOCK_SIZE_M
+            and topk == 2 and gating.dtype in _LOGIT_TAGS):
+        # The common case in one C-ABI call: the library issues the six steps itself.
+        ptrs = ws.get("ptrs")
+        if ptrs is None:
+            ptrs = ws["ptrs"] = (ws["topk_weights"].data_ptr(), ws["topk_ids"].data_ptr(),
+                                 ws["sorted_ids"].data_ptr(), ws["expert_ids"].data_ptr(),
+                                 ws["num_post_pad"].data_ptr(), ws["align_ws"].data_ptr(),
+                                 ws["align_ws"].numel() * 4, ws["a_sorted"].data_ptr(),
+                                 ws["act"].data_ptr(), ws["cache3"].data_ptr())
+            ws["launches"] = 5 + (3 if num_tokens * topk > _C.align_single_pass_max() else 1)
+        with torch.cuda.device(dev):
+            _lib.check(lib.b200moe_fused_experts(
+                hidden_states.data_ptr(), gating.data_ptr(), _LOGIT_TAGS[gating.dtype], w1.data_ptr(),
+                w2.data_ptr(), output.data_ptr(), num_tokens, num_experts, topk, hidden, inter,
+                int(renormalize), *ptrs, torch.cuda.current_stream(dev).cuda_stream), "fused_experts")
+        _lib.count_launches(ws["launches"])
+        return output
 
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream

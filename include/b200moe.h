@@ -389,6 +389,34 @@ int b200moe_paged_attn_varlen(const void* q, const void* k_cache, const void* v_
                               size_t workspace_bytes, b200moe_stream_t stream);
 
 /*
+ * The whole layer in one call: router (softmax, top-2, optional renormalisation) -> token alignment
+ * with block 128 (writes its own padding) -> gather of the routed rows -> grouped GEMM w13 + SwiGLU
+ * -> grouped GEMM w2 x routing weight -> combine, issued back to back on `stream` by the entry
+ * points above.  Replaces fused_experts of layers/moe/fused_moe.py:170-293 for bf16 tensors and
+ * top_k = 2; `output` may be `hidden_states` (the in-place use of FusedMoE.forward,
+ * layers/moe/mixtral_moe.py:103-112).
+ *
+ *   hidden_states [num_tokens, hidden] bf16, gating_output [num_tokens, num_experts] of logits_dtype,
+ *   w13 [num_experts, 2*inter, hidden] bf16 (gate rows first), w2 [num_experts, hidden, inter] bf16,
+ *   output [num_tokens, hidden] bf16.
+ * Scratch, all caller-owned, with R = b200moe_fused_experts_rows(num_tokens, top_k, num_experts):
+ *   topk_weights f32 [num_tokens * top_k], topk_ids i32 [num_tokens * top_k], sorted_token_ids i32 [R],
+ *   expert_ids i32 [ceil(R / 128)], num_tokens_post_pad i32 [1],
+ *   align_workspace of b200moe_align_workspace_bytes(num_tokens * top_k, num_experts) bytes (may be
+ *   NULL when that is 0), a_sorted bf16 [R, hidden], act bf16 [R, inter],
+ *   pair_rows bf16 [num_tokens * top_k, hidden].
+ * Nothing in the scratch has to be initialised.  No allocation, no host synchronisation.
+ */
+size_t b200moe_fused_experts_rows(int64_t num_tokens, int top_k, int num_experts);
+int b200moe_fused_experts(const void* hidden_states, const void* gating_output, int logits_dtype,
+                          const void* w13, const void* w2, void* output, int64_t num_tokens,
+                          int num_experts, int top_k, int64_t hidden, int64_t inter, int renormalize,
+                          float* topk_weights, int32_t* topk_ids, int32_t* sorted_token_ids,
+                          int32_t* expert_ids, int32_t* num_tokens_post_pad, void* align_workspace,
+                          size_t align_workspace_bytes, void* a_sorted, void* act, void* pair_rows,
+                          b200moe_stream_t stream);
+
+/*
  * Device-side status word of the grouped GEMMs.  Their waits on memory barriers are bounded; a
  * wait that runs out records a non-zero code here and the kernel returns.  Reading synchronises
  * with the device.  Returns the code (0 = no error) or a negative B200MOE_ERR_*; `reset` != 0

@@ -370,6 +370,33 @@ def test_layer_block_sizes_agree_bit_for_bit(T):
     check_layer(inp, wl)
 
 
+@pytest.mark.parametrize("T,logit_dtype", [(3, torch.float32), (700, torch.bfloat16), (40000, torch.float32)])
+def test_one_call_entry_point_matches_the_step_by_step_path(T, logit_dtype):
+    """``b200moe_fused_experts`` (the layer in one C-ABI call, what ``fused_experts`` uses by default)
+    against the same six steps issued one by one from Python (the path taken while per-kernel
+    timing is on): same bits.  T=40000 gives more pair indices than one alignment launch takes."""
+    from electrock_infer_b200.layers.moe import fused_moe as fm
+    wl = MoEWorkload("t", T, 256, 128, seed=7 + T, logit_bias=(1, 0, 0, 0, 0, 0, -1, -3))
+    inp = make_inputs(wl)
+    dev_in = [inp[k].to(torch.bfloat16).to(DEV) for k in ("x", "w13", "w2")]
+    logits = inp["logits"].to(logit_dtype).to(DEV)
+    before = _lib.launch_count()
+    one_call = fused_experts(dev_in[0].clone(), dev_in[1], dev_in[2], logits, 2, inplace=True)
+    assert _lib.launch_count() - before == (8 if 2 * T > _C.align_single_pass_max() else 6)
+    fm.enable_kernel_timing(True)
+    try:
+        stepwise = fused_experts(dev_in[0].clone(), dev_in[1], dev_in[2], logits, 2, inplace=True)
+        assert set(fm.collect_kernel_timings()) >= {"topk_softmax", "grouped_gemm_w13_swiglu", "moe_sum"}
+    finally:
+        fm.enable_kernel_timing(False)
+    torch.cuda.synchronize()
+    assert gemm_status() == 0 and torch.equal(one_call, stepwise)
+    want = moe_oracle.moe_block_ref(inp["x"].to(torch.bfloat16)[:512], inp["w13"].to(torch.bfloat16),
+                                    inp["w2"].to(torch.bfloat16), logits[:512].float().cpu())
+    st = moe_oracle.error_stats(one_call[:512].cpu().float(), want)
+    assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, st
+
+
 def test_layer_skewed_and_empty_experts():
     wl = MoEWorkload("skew", 700, 256, 512, seed=3, logit_bias=(6, 5, 0, 0, -20, -20, -20, -20))
     inp = make_inputs(wl)
