@@ -18,6 +18,7 @@ I32, I64, I16, I8, U8 = 0, 1, 2, 3, 4
 # (restype, argtypes) of every exported symbol, in header order.
 SIGNATURES = {
     "b200moe_abi_version": (c_int, []),
+    "b200moe_kernel_launch_count": (c_int64, []),
     "b200moe_last_error": (c_char_p, []),
     "b200moe_topk_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
                                      c_int, c_void_p]),
@@ -87,13 +88,16 @@ _launches = 0
 
 
 def count_launches(n: int = 1) -> None:
-    """Book-keeping for benchmarks: kernels launched through this binding so far."""
+    """Kept for callers that announce their launches; the count that ``launch_count`` reports is
+    the library's own (``b200moe_kernel_launch_count``), which needs no announcement."""
     global _launches
     _launches += n
 
 
 def launch_count() -> int:
-    return _launches
+    """Kernels the library has launched in this process, counted by the library itself at every
+    launch site (both kernels of a grouped-GEMM launch pair included)."""
+    return int(load().b200moe_kernel_launch_count())
 
 
 def load() -> ctypes.CDLL:

@@ -621,6 +621,8 @@ int run(const void* ids_v, int64_t numel, int E, int bs, int32_t* sorted, int64_
   launch_pdl(align_count_kernel<T>, segs, dim3(kSegThreads), 0, st, ids, numel, E, seg);
   launch_pdl(align_scan_kernel, dim3(1), dim3(kThreads), 0, st, seg, nseg, E, bs, meta, npp,
              offsets);
+  note_launch();  // count and scan; the scatter launch is counted by check_launch below
+  note_launch();
   launch_pdl(align_scatter_kernel<T>, segs, dim3(kSegThreads), 0, st, ids, numel, E, bs,
              static_cast<const int32_t*>(seg), static_cast<const int32_t*>(meta), sorted, cap,
              expert_ids, fill);

@@ -1,4 +1,5 @@
 // Error reporting and device queries shared by every entry point of libb200moe.
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -6,7 +7,10 @@
 namespace b200moe {
 namespace {
 thread_local char g_last_error[512] = "";
+std::atomic<long long> g_launches{0};
 }
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -35,5 +39,9 @@ int sm_count() {
 }  // namespace b200moe
 
 extern "C" int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
+
+extern "C" int64_t b200moe_kernel_launch_count(void) {
+  return b200moe::g_launches.load(std::memory_order_relaxed);
+}
 
 extern "C" const char* b200moe_last_error(void) { return b200moe::g_last_error; }

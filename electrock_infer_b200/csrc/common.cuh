@@ -16,10 +16,15 @@ namespace b200moe {
 int fail(int code, const char* fmt, ...);
 void clear_error();
 
-// Reports a failed launch (cudaGetLastError) as B200MOE_ERR_CUDA.
+// Counts a kernel launch of this library (read by b200moe_kernel_launch_count()).
+void note_launch();
+
+// Called directly after every kernel launch: counts it and reports a failed launch
+// (cudaGetLastError) as B200MOE_ERR_CUDA.
 inline int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  note_launch();
   return B200MOE_OK;
 }
 

@@ -57,6 +57,11 @@ typedef void* b200moe_stream_t;
 /* ABI version of the loaded library (B200MOE_ABI_VERSION at build time). */
 int b200moe_abi_version(void);
 
+/* Kernels this library has launched in this process so far (every entry point counts its own
+ * launches, including the second kernel of a grouped-GEMM launch pair): for benchmarks that report
+ * how many of the library's kernels ran inside a timed region. */
+int64_t b200moe_kernel_launch_count(void);
+
 /* Text of the last error raised on the calling thread ("" if none). */
 const char* b200moe_last_error(void);
 
