@@ -398,6 +398,46 @@ def test_one_call_entry_point_matches_the_step_by_step_path(T, logit_dtype):
     assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, st
 
 
+def test_scratch_is_sized_by_capacity_bucket_and_reused():
+    """A serving loop changes its batch size every step: after the largest batch has been seen (or
+    reserved), smaller batches must run in a prefix of the same scratch without allocating, and
+    give the results they give on their own."""
+    from electrock_infer_b200.layers.moe import fused_moe as fm
+    H, I = 768, 384   # a shape no other test uses, so the scratch entry is this test's own
+    wl = MoEWorkload("bucket", 1000, H, I, seed=77, logit_bias=(1, 0, 0, 0, 0, 0, -1, -3))
+    inp = make_inputs(wl)
+    w13, w2 = inp["w13"].to(torch.bfloat16).to(DEV), inp["w2"].to(torch.bfloat16).to(DEV)
+    x_all, logits_all = inp["x"].to(torch.bfloat16).to(DEV), inp["logits"].to(DEV)
+    assert fm.capacity_bucket(700) == fm.capacity_bucket(1000) == 1024
+    fm.reserve_workspace(DEV, 700, 2, 8, H, I)          # sizes the bucket of 1024 tokens
+    want = moe_oracle.moe_block_ref(inp["x"].to(torch.bfloat16), inp["w13"].to(torch.bfloat16),
+                                    inp["w2"].to(torch.bfloat16), inp["logits"])
+    torch.cuda.synchronize()
+    for T in (700, 300, 1000, 1, 513, 1024 - 24):
+        x, lg = x_all[:T].clone(), logits_all[:T].contiguous()
+        before = torch.cuda.memory_allocated()
+        out = fused_experts(x, w13, w2, lg, 2, inplace=True)
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before, f"T={T} allocated scratch"
+        st = moe_oracle.error_stats(out.cpu().float(), want[:T])
+        assert st["max_abs"] <= MAX_ABS and st["rel_fro"] <= REL_FRO, (T, st)
+        del x, out   # the next step's measurement must not see this step's tensors being freed
+    assert gemm_status() == 0
+    # A batch beyond the bucket grows the scratch once; the next batches reuse the larger one.
+    wl2 = MoEWorkload("bucket2", 1500, H, I, seed=78)
+    inp2 = make_inputs(wl2)
+    x2 = inp2["x"].to(torch.bfloat16).to(DEV)
+    logits2 = inp2["logits"].to(DEV)
+    grown = fused_experts(x2.clone(), w13, w2, logits2, 2, inplace=True)
+    torch.cuda.synchronize()
+    del grown
+    x, lg = x_all[:900].clone(), logits_all[:900].contiguous()
+    before = torch.cuda.memory_allocated()
+    out = fused_experts(x, w13, w2, lg, 2, inplace=True)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before
+
+
 def test_layer_skewed_and_empty_experts():
     wl = MoEWorkload("skew", 700, 256, 512, seed=3, logit_bias=(6, 5, 0, 0, -20, -20, -20, -20))
     inp = make_inputs(wl)
