@@ -44,7 +44,7 @@ def aligned(ids_flat, E, block_m=BLOCK_SIZE_M):
 @pytest.mark.parametrize("block_m,tiling", TILINGS)
 @pytest.mark.parametrize("T,H,I,E", [(100, 256, 128, 8), (300, 512, 1024, 8), (37, 64, 256, 3),
                                      (1000, 1024, 512, 8), (1, 256, 128, 8), (3000, 512, 256, 8),
-                                     (2500, 128, 128, 2)])
+                                     (2500, 128, 128, 2), (2100, 256, 128, 1)])
 def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m, tiling):
     lib = _lib.load()
     _lib.check(lib.b200moe_gemm_set_tiling(tiling), "set_tiling")
@@ -80,7 +80,8 @@ def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m, tiling):
 
 @pytest.mark.parametrize("block_m,tiling", TILINGS)
 @pytest.mark.parametrize("T,H,I,E", [(100, 256, 128, 8), (300, 512, 1024, 8), (37, 256, 64, 3),
-                                     (1000, 1024, 512, 8), (3000, 512, 256, 8), (2500, 256, 128, 2)])
+                                     (1000, 1024, 512, 8), (3000, 512, 256, 8), (2500, 256, 128, 2),
+                                     (2100, 256, 128, 1)])
 def test_grouped_gemm_w2_scale(T, H, I, E, block_m, tiling):
     lib = _lib.load()
     _lib.check(lib.b200moe_gemm_set_tiling(tiling), "set_tiling")
