@@ -36,3 +36,33 @@ def test_reference_arm_prints_one_json_line():
 
 def test_reference_arm_is_silent_on_other_ranks():
     assert run_bench({"RANK": "1", "LOCAL_RANK": "1", "WORLD_SIZE": "2"}) == ""
+
+
+def test_roofline_fraction_is_against_the_burst_peak():
+    """``roofline.frac`` divides by the measured burst peak (the sustained figure is a named extra),
+    the bound switches to HBM where streaming the weights takes longer than the FLOPs, and the
+    traffic figures scale the algorithmic bytes by the per-kernel ncu ratios."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_module", REPO / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    peaks = {"hbm_gbs": 6453.1, "bf16_tflops": 1706.6, "bf16_tflops_sustained": 1411.1, "source": "measured"}
+    wl = bench.WORKLOADS["mixtral_prefill_t8192_skew"]
+    roof, extra = bench.gemm_roofline(wl, "single", 1, {"grouped_gemm_w13_swiglu": 2.8, "grouped_gemm_w2_scale": 1.4,
+                                                        "moe_sum": 0.036}, peaks)
+    flops = 4 * 4096 * 14336 * 2 * 8192
+    assert roof["bound"] == "tensor" and roof["peak"] == 1706.6 and roof["unit"] == "TFLOP/s"
+    assert abs(roof["achieved"] - flops / 2.8e-3 / 1e12) < 1e-6
+    assert abs(roof["frac"] - roof["achieved"] / 1706.6) < 1e-12
+    assert abs(roof["frac_of_sustained"] - roof["achieved"] / 1411.1) < 1e-12
+    w13_bytes = 8 * 2 * 14336 * 4096 * 2 + 8192 * 2 * (4096 + 14336) * 2
+    assert abs(roof["traffic"] - bench.NCU_TRAFFIC_RATIO["grouped_gemm_w13_swiglu"] * w13_bytes) < 1
+    assert extra["moe_sum_frac_of_hbm"] == extra["moe_sum_gbs"] / 6453.1
+    # Expert parallel over 8: an eighth of the tokens' pairs and one expert land on a rank.
+    roof8, _ = bench.gemm_roofline(bench.WORKLOADS["mixtral_parallel_t16384"], "ep", 8,
+                                   {"grouped_gemm_w13_swiglu": 0.66}, peaks)
+    assert abs(roof8["achieved"] - 4 * 4096 * 14336 * 2 * 2048 / 0.66e-3 / 1e12) < 1e-6
+    # Decode-sized batch: weight streaming is the longer floor.
+    small, _ = bench.gemm_roofline(bench.WORKLOADS["mixtral_decode_t256"], "single", 1,
+                                   {"grouped_gemm_w13_swiglu": 0.31}, peaks)
+    assert small["bound"] == "hbm" and small["peak"] == 6453.1 and 0.9 < small["frac"] < 1.0
