@@ -140,6 +140,26 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       "r"(c1)
       : "memory");
 }
+// Bulk tensor store of a box from shared memory (bulk-group completion), and its bookkeeping.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1)
+      : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Shared memory of every bulk store issued by this thread has been read (it may be overwritten).
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// Every bulk store issued by this thread is complete.
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// Makes this thread's ordinary shared-memory writes visible to the bulk-copy engine.
+__device__ __forceinline__ void fence_smem_to_async_proxy() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
 // Four rows of a 2-D tensor (box = 64 columns x 1 row) gathered into four consecutive 128-byte
 // rows of shared memory; the 128-byte swizzle is a function of the destination address, so 32
 // such gathers lay out a 128-row tile exactly like one tiled box.
@@ -303,6 +323,7 @@ struct GemmParams {
   int m_group;                   // M blocks per L2-resident group of an expert (0: no grouping)
   int top_k;                     // kW13Gather: A row of slot s is sorted[s] / top_k
   int num_src_rows;              // kW13Gather: rows of the token tensor
+  int tma_store;                 // kW13: rows leave the SM as bulk tensor stores (half_n % 64 == 0)
   int dual_min_blocks;           // > 0: the one-block and the two-block kernel are both launched and
                                  // decide on the device which of them runs (two_block_tiles_win)
 };
@@ -353,6 +374,23 @@ __device__ __forceinline__ void swiglu_chunk(const uint32_t (&g)[N], const uint3
   }
 }
 
+// The same for the bulk-store path: the staging area is 32 dense rows of 128 bytes in the 128-byte
+// swizzle the tensor map of the output expects (16-byte piece c of row r sits at piece c ^ (r & 7)),
+// which also keeps the lanes' 16-byte writes on distinct banks.  `first_piece` is 0 or 4.
+__device__ __forceinline__ void swiglu_chunk_swizzled(const uint32_t (&g)[32], const uint32_t (&u)[32],
+                                                      uint8_t* stage_out, int row, int first_piece) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      o[i] = pack_bf16(silu_mul(__uint_as_float(g[8 * q + 2 * i]), __uint_as_float(u[8 * q + 2 * i])),
+                       silu_mul(__uint_as_float(g[8 * q + 2 * i + 1]), __uint_as_float(u[8 * q + 2 * i + 1])));
+    *reinterpret_cast<uint4*>(stage_out + row * 128 + (((first_piece + q) ^ (row & 7)) << 4)) =
+        make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // Writes `width` (<= 64, a multiple of 8) staged columns of the warp's 32 rows to consecutive rows
 // of the output, eight lanes per row.
 __device__ __forceinline__ void flush_rows(const uint8_t* stage_out, __nv_bfloat16* dst, long long ld,
@@ -375,8 +413,9 @@ __device__ __forceinline__ void flush_rows(const uint8_t* stage_out, __nv_bfloat
 // accumulator, twice the time its arithmetic needs).  So 32 gate and 32 up columns are loaded at
 // a time into one of two register sets, and the next set's loads are in flight while the current
 // one goes through the special-function unit.
-__device__ __forceinline__ void drain_w13(const GemmParams& p, uint32_t taddr, uint8_t* stage_out,
-                                          int m_block, int n_tile, int quarter, int lane) {
+__device__ __forceinline__ void drain_w13(const GemmParams& p, const CUtensorMap* tmap_out,
+                                          uint32_t taddr, uint8_t* stage_out, int m_block,
+                                          int n_tile, int quarter, int lane) {
 #ifdef B200MOE_MEASURE_WITHOUT_EPILOGUE  // measurement builds only: results are not written
   return;
 #endif
@@ -389,6 +428,33 @@ __device__ __forceinline__ void drain_w13(const GemmParams& p, uint32_t taddr, u
   if (wide > 0) {
     tmem_ld_32x32(taddr, ga);
     tmem_ld_32x32(taddr + p.half_n, ua);
+  }
+  if (p.tma_store) {
+    // 64 output columns of the warp's 32 rows leave as ONE bulk tensor store issued by one lane:
+    // the warp goes on with the next columns while the copy engine drains the staging area,
+    // instead of pushing sixteen 16-byte store instructions per lane through the load/store path
+    // that the operand loads keep busy.  half_n is a multiple of 64 here.
+    const int out_row = m_block * kBlockM + quarter * 32;
+    const int out_col = n_tile * p.half_n;
+#pragma unroll 1
+    for (int j = 0; j < wide; j += 2) {
+      tmem_ld_wait();
+      tmem_ld_32x32(taddr + (j + 1) * 32, gb);
+      tmem_ld_32x32(taddr + p.half_n + (j + 1) * 32, ub);
+      if (lane == 0) tma_store_wait_read();  // the previous store has read the staging area
+      __syncwarp();
+      swiglu_chunk_swizzled(ga, ua, stage_out, lane, 0);
+      tmem_ld_wait();
+      if (j + 2 < wide) {
+        tmem_ld_32x32(taddr + (j + 2) * 32, ga);
+        tmem_ld_32x32(taddr + p.half_n + (j + 2) * 32, ua);
+      }
+      swiglu_chunk_swizzled(gb, ub, stage_out, lane, 4);
+      fence_smem_to_async_proxy();
+      __syncwarp();
+      if (lane == 0) tma_store_2d(tmap_out, stage_out, out_col + j * 32, out_row);
+    }
+    return;
   }
 #pragma unroll 1
   for (int j = 0; j < wide; j += 2) {
@@ -485,7 +551,9 @@ __device__ __forceinline__ void drain_w2(const GemmParams& p, uint32_t taddr, ui
 template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_out,   // kW13 with p.tma_store: act
+                    const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
   __shared__ uint32_t tmem_slot;
@@ -666,9 +734,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * kBlockN);
-      uint8_t* stage_out = smem + kStages * kStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
+      // Bulk stores read dense 128-byte rows from a 1024-byte aligned area; the other paths use
+      // rows padded to 144 bytes.
+      uint8_t* stage_out = smem + kStages * kStageBytes +
+                           (warp - 2) * ((kIsW13 && p.tma_store) ? 32 * 128 : 32 * kOutStageRowBytes);
       if (kIsW13) {
-        drain_w13(p, taddr, stage_out, c.m_block, c.n_tile, quarter, lane);
+        drain_w13(p, &tmap_out, taddr, stage_out, c.m_block, c.n_tile, quarter, lane);
       } else {
         drain_w2(p, taddr, stage_out, c.m_block, c.n_tile, quarter, lane);
       }
@@ -677,6 +748,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
     }
+    if (kIsW13 && p.tma_store && lane == 0) tma_store_wait_all();  // before shared memory goes away
   }
 
   // ------------------------------------------------------------------ teardown
@@ -895,7 +967,9 @@ template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box of 128 rows
                          const __grid_constant__ CUtensorMap tmap_a2,   // box of 256 rows
-                         const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_out,  // kW13 with p.tma_store: act
+                         const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[kDualStages], empty_bar[kDualStages], tmem_full_bar[2],
       tmem_empty_bar[2];
@@ -1157,7 +1231,8 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quarter = warp & 3;               // TMEM lanes this warp may read: 32*quarter ..
-    uint8_t* stage_out = smem + kDualStages * kDualStageBytes + (warp - 2) * 32 * kOutStageRowBytes;
+    uint8_t* stage_out = smem + kDualStages * kDualStageBytes +
+                         (warp - 2) * ((kIsW13 && p.tma_store) ? 32 * 128 : 32 * kOutStageRowBytes);
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
     long long it = 0, cyc_drain = 0, drains = 0;
@@ -1178,7 +1253,7 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
         if (b < t.m_count) {
           B200MOE_CYCLES_BEGIN(d0);
           if (kIsW13) {
-            drain_w13(p, taddr + b * kBlockN, stage_out, t.m_block + b, t.n_tile, quarter, lane);
+            drain_w13(p, &tmap_out, taddr + b * kBlockN, stage_out, t.m_block + b, t.n_tile, quarter, lane);
           } else {
             drain_w2(p, taddr + b * kBlockN, stage_out, t.m_block + b, t.n_tile, quarter, lane);
           }
@@ -1200,6 +1275,7 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
 #endif
     (void)cyc_drain;
     (void)drains;
+    if (kIsW13 && p.tma_store && lane == 0) tma_store_wait_all();  // before shared memory goes away
   }
 
   // ------------------------------------------------------------------ teardown
@@ -1559,7 +1635,8 @@ int make_tmap(CUtensorMap* map, const void* base, long long rows, long long cols
 }
 
 template <int kMode>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const GemmParams& p,
+           cudaStream_t st) {
   // The attribute belongs to the function in the current context; setting it on every launch is
   // cheap and keeps processes that drive several devices correct.
   const cudaError_t attr_err = cudaFuncSetAttribute(
@@ -1567,25 +1644,28 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cu
   if (attr_err != cudaSuccess)
     return fail(B200MOE_ERR_CUDA, "grouped_gemm: cannot reserve %d bytes of shared memory: %s",
                 kSmemBytes, cudaGetErrorString(attr_err));
-  launch_pdl(grouped_gemm_kernel<kMode>, dim3(sm_count()), dim3(kThreads), kSmemBytes, st, ta, tb, p);
+  launch_pdl(grouped_gemm_kernel<kMode>, dim3(sm_count()), dim3(kThreads), kSmemBytes, st, ta, tb, tout,
+             p);
   return check_launch("grouped_gemm");
 }
 
 template <int kMode>
 int launch_dual(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb,
-                const GemmParams& p, cudaStream_t st) {
+                const CUtensorMap& tout, const GemmParams& p, cudaStream_t st) {
   const cudaError_t attr_err = cudaFuncSetAttribute(
       grouped_gemm_dual_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDualSmemBytes);
   if (attr_err != cudaSuccess)
     return fail(B200MOE_ERR_CUDA, "grouped_gemm: cannot reserve %d bytes of shared memory: %s",
                 kDualSmemBytes, cudaGetErrorString(attr_err));
   launch_pdl(grouped_gemm_dual_kernel<kMode>, dim3(sm_count()), dim3(kThreads), kDualSmemBytes, st,
-             ta, ta2, tb, p);
+             ta, ta2, tb, tout, p);
   return check_launch("grouped_gemm (two-block tiles)");
 }
 
 // Tiling of the one-CTA kernels: 0 = chosen by batch size, 1 = one M block per tile, 2 = two.
 std::atomic<int> g_tiling{0};
+// Whether the first GEMM's epilogue uses bulk tensor stores (b200moe_gemm_set_act_stores).
+std::atomic<int> g_tma_act_stores{1};
 
 // Two-block tiles pay off once most experts hold several M blocks: the weight stage is then
 // shared by two blocks almost everywhere.  With one block per expert (decode-sized batches) every
@@ -1620,12 +1700,12 @@ int make_dual_maps(DualMaps* m, const void* a, long long a_rows, long long k, co
 
 template <int kMode>
 int launch_chosen(TileChoice choice, int min_blocks, const CUtensorMap& ta, const CUtensorMap& tb,
-                  const DualMaps& dm, GemmParams p, cudaStream_t st) {
-  if (choice == kOneBlock) return launch<kMode>(ta, tb, p, st);
-  if (choice == kTwoBlock) return launch_dual<kMode>(dm.a, dm.a2, dm.b, p, st);
+                  const CUtensorMap& tout, const DualMaps& dm, GemmParams p, cudaStream_t st) {
+  if (choice == kOneBlock) return launch<kMode>(ta, tb, tout, p, st);
+  if (choice == kTwoBlock) return launch_dual<kMode>(dm.a, dm.a2, dm.b, tout, p, st);
   p.dual_min_blocks = min_blocks;
-  if (int rc = launch<kMode>(ta, tb, p, st)) return rc;
-  return launch_dual<kMode>(dm.a, dm.a2, dm.b, p, st);
+  if (int rc = launch<kMode>(ta, tb, tout, p, st)) return rc;
+  return launch_dual<kMode>(dm.a, dm.a2, dm.b, tout, p, st);
 }
 
 template <int kMode>
@@ -1749,7 +1829,13 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   set_width(&p, 2 * half_n);
   p.m_group = m_group_for(hidden * 2);
   if (block_m == kPairBlockM) return launch_pair<kW13>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW13>(tiles, dual_min_blocks, ta, tb, dm, p, static_cast<cudaStream_t>(stream));
+  // Output rows leave as bulk tensor stores of 32 rows x 64 columns where the tile width allows.
+  CUtensorMap tout = ta;
+  p.tma_store = (half_n % 64 == 0 && g_tma_act_stores.load(std::memory_order_relaxed)) ? 1 : 0;
+  if (p.tma_store)
+    if (int rc = make_tmap(&tout, act, sorted_capacity, inter, 32, name)) return rc;
+  return launch_chosen<kW13>(tiles, dual_min_blocks, ta, tb, tout, dm, p,
+                             static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w13_swiglu_gather(
@@ -1798,7 +1884,7 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu_gather(
   p.m_group = m_group_for(hidden * 2);
   p.top_k = top_k;
   p.num_src_rows = static_cast<int>(num_tokens);
-  return launch<kW13Gather>(ta, tb, p, static_cast<cudaStream_t>(stream));
+  return launch<kW13Gather>(ta, tb, ta, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, void* out,
@@ -1855,7 +1941,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, dm, p, static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, ta, dm, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w2_scale_peer(
@@ -1913,7 +1999,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, dm, p, static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, ta, dm, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t b200moe_gemm_two_block_schedule(const int32_t* blocks_per_expert, int num_experts,
@@ -1958,6 +2044,11 @@ extern "C" int64_t b200moe_gemm_two_block_schedule(const int32_t* blocks_per_exp
     }
   }
   return written;
+}
+
+extern "C" int b200moe_gemm_set_act_stores(int bulk) {
+  b200moe::g_tma_act_stores.store(bulk ? 1 : 0, std::memory_order_relaxed);
+  return B200MOE_OK;
 }
 
 extern "C" int b200moe_gemm_set_tiling(int mode) {

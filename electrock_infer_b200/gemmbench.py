@@ -7,7 +7,8 @@ the two-block kernel when the loaded library is a measurement build.
 A case is ``routing:tokens``: ``skew`` is the routing of the benchmark workload
 (mixtral_prefill_t8192_skew), ``uni`` the near-uniform routing of mixtral_parallel_t16384.
 Tilings: 0 the library's own choice, 1 one M block per tile, 2 two M blocks per tile, 3 CTA pairs
-(block_m 256).  Each variant runs ``--steps`` layer calls with a CUDA-event pair around every
+(block_m 256); add 10 for the first GEMM's epilogue with per-lane stores instead of bulk tensor
+stores.  Each variant runs ``--steps`` layer calls with a CUDA-event pair around every
 launch; the variants are interleaved ``--reps`` times after one unmeasured round, and the median of
 the per-repetition means is printed (under the board's power cap a kernel's time depends on what
 ran before it, so only numbers of one run compare).  One JSON line per case and tiling.
@@ -50,8 +51,9 @@ def run_tilings(cases, tilings, steps: int, reps: int, dev) -> None:
         try:
             for rep in range(reps + 1):
                 for tiling in tilings:
-                    fm.FORCE_BLOCK_M = 256 if tiling == 3 else 128
-                    _lib.check(lib.b200moe_gemm_set_tiling(tiling if tiling < 3 else 0), "set_tiling")
+                    fm.FORCE_BLOCK_M = 256 if tiling % 10 == 3 else 128
+                    _lib.check(lib.b200moe_gemm_set_tiling(tiling % 10 if tiling % 10 < 3 else 0), "set_tiling")
+                    lib.b200moe_gemm_set_act_stores(0 if tiling >= 10 else 1)
                     fm.enable_kernel_timing(True)
                     for _ in range(steps):
                         x.copy_(x0)
@@ -64,6 +66,7 @@ def run_tilings(cases, tilings, steps: int, reps: int, dev) -> None:
         finally:
             fm.FORCE_BLOCK_M = None
             lib.b200moe_gemm_set_tiling(0)
+            lib.b200moe_gemm_set_act_stores(1)
         flops13 = 4 * wl.hidden * wl.inter * wl.top_k * tokens
         for tiling in tilings:
             k13 = statistics.median(seen[tiling]["w13"])
@@ -127,7 +130,7 @@ def run_cycles(cases, steps: int, dev) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("cases", nargs="*", default=["skew:8192", "uni:16384"])
-    ap.add_argument("--tilings", type=int, nargs="+", default=[1, 2], choices=[0, 1, 2, 3])
+    ap.add_argument("--tilings", type=int, nargs="+", default=[1, 2], choices=[0, 1, 2, 3, 10, 11, 12, 13])
     ap.add_argument("--steps", type=int, default=15)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--lib", default=None, help="another build of the library to load")

@@ -454,6 +454,14 @@ int b200moe_gemm_measured_cycles(uint64_t* out8, int reset);
 int b200moe_gemm_set_tiling(int mode);
 
 /*
+ * How the first grouped GEMM writes its output, a process-wide setting for benchmarks and tests:
+ * non-zero (default) = bulk tensor stores of 32 rows x 64 columns issued by one lane per epilogue
+ * warp, where the tile is a multiple of 64 columns wide; 0 = 16-byte stores from every lane.  Same
+ * bits either way.  No counterpart in the reference.
+ */
+int b200moe_gemm_set_act_stores(int bulk);
+
+/*
  * Host-side view of the work list of the two-block tiling, for tests and tuning: the items that
  * CTA `cta` of `grid` processes, in order, when the experts hold `blocks_per_expert[e]` M blocks
  * of 128 rows, the output has `n_tiles` N tiles, `m_group` is the L2 grouping of M blocks and

@@ -44,10 +44,36 @@ def aligned(ids_flat, E, block_m=BLOCK_SIZE_M):
 @pytest.mark.parametrize("block_m,tiling", TILINGS)
 @pytest.mark.parametrize("T,H,I,E", [(100, 256, 128, 8), (300, 512, 1024, 8), (37, 64, 256, 3),
                                      (1000, 1024, 512, 8), (1, 256, 128, 8), (3000, 512, 256, 8),
-                                     (2500, 128, 128, 2), (2100, 256, 128, 1)])
+                                     (2500, 128, 128, 2), (2100, 256, 128, 1), (700, 256, 384, 4)])
 def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m, tiling):
+    _lib.check(_lib.load().b200moe_gemm_set_tiling(tiling), "set_tiling")
+    got, want, used = run_w13(T, H, I, E, block_m)
+    st = moe_oracle.error_stats(got[:used], want)
+    assert st["rel_fro"] < 4e-3 and st["max_abs"] < 2e-2 * max(st["ref_max_abs"], 1.0), st
+    assert (got[used:] == 9.0).all(), "rows beyond num_tokens_post_pad were written"
+
+
+@pytest.mark.parametrize("tiling", [1, 2])
+@pytest.mark.parametrize("T,H,I,E", [(300, 512, 1024, 8), (3000, 512, 256, 8), (700, 256, 384, 4)])
+def test_w13_bulk_tensor_stores_and_per_lane_stores_agree_bit_for_bit(T, H, I, E, tiling):
+    """The first GEMM's epilogue has two ways out of the SM (bulk tensor stores of 32 x 64 pieces where
+    the tile's width is a multiple of 64 columns, 16-byte stores per lane otherwise): same bits."""
     lib = _lib.load()
     _lib.check(lib.b200moe_gemm_set_tiling(tiling), "set_tiling")
+    try:
+        lib.b200moe_gemm_set_act_stores(0)
+        plain, want, used = run_w13(T, H, I, E, 128)
+        lib.b200moe_gemm_set_act_stores(1)
+        bulk, _, _ = run_w13(T, H, I, E, 128)
+    finally:
+        lib.b200moe_gemm_set_act_stores(1)
+    assert torch.equal(plain, bulk)
+    st = moe_oracle.error_stats(bulk[:used], want)
+    assert st["rel_fro"] < 4e-3, st
+
+
+def run_w13(T, H, I, E, block_m):
+    lib = _lib.load()
     g = torch.Generator().manual_seed(T + H)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)
     w13 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).to(torch.bfloat16)
@@ -73,9 +99,7 @@ def test_grouped_gemm_w13_swiglu(T, H, I, E, block_m, tiling):
         if m.any():
             y = a_sorted[:used][m].float() @ w13[ex].float().T
             want[m] = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
-    st = moe_oracle.error_stats(got[:used], want)
-    assert st["rel_fro"] < 4e-3 and st["max_abs"] < 2e-2 * max(st["ref_max_abs"], 1.0), st
-    assert (got[used:] == 9.0).all(), "rows beyond num_tokens_post_pad were written"
+    return got, want, used
 
 
 @pytest.mark.parametrize("block_m,tiling", TILINGS)
