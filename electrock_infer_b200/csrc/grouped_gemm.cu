@@ -68,7 +68,7 @@ enum Mode { kW13 = 0, kW2 = 1, kW13Gather = 2 };
 // Device status word: 0 = fine; otherwise (role << 8) | barrier kind of the wait that ran out.
 __device__ int g_gemm_status = 0;
 
-// Cycle accounting of the two-block kernel, compiled in with -DB200MOE_MEASURE_CYCLES only (a
+// Cycle accounting of the one-block and the two-block kernel, compiled in with -DB200MOE_MEASURE_CYCLES only (a
 // measurement build: the counters cost a few clock reads per K step).  Summed over all CTAs:
 //   [0] cycles epilogue warp 2 spent draining accumulators   [1] accumulators drained by it
 //   [2] cycles the MMA thread waited for operand stages       [3] ... for a free accumulator
@@ -111,6 +111,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 // Bounded wait.  Returns false when the barrier did not flip in time or another role aborted.
+// Backing off between polls (__nanosleep of 100-500 ns in the epilogue's, the producer's or the MMA
+// thread's waits) was measured and changes nothing beyond run-to-run noise (first GEMM at T = 8192:
+// 2.96-3.02 ms with and without, alternating processes on one GPU).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int who) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -695,14 +698,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       long long it = 0;
+      long long cyc_full = 0, cyc_tmem = 0;
+      B200MOE_CYCLES_BEGIN(loop_begin);
       for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
         const int acc = static_cast<int>(it & 1);
         const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+        B200MOE_CYCLES_BEGIN(w0);
         if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, 0x201)) { ok = false; break; }
+        B200MOE_CYCLES_ADD(cyc_tmem, w0);
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kBlockN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          B200MOE_CYCLES_BEGIN(w1);
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, 0x202)) { ok = false; break; }
+          B200MOE_CYCLES_ADD(cyc_full, w1);
           const uint32_t sa = smem_u32(smem + stage * kStageBytes);
           const uint32_t sb = sa + kABytes;
 #pragma unroll
@@ -716,6 +725,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (ok) umma_commit(&tmem_full_bar[acc]);  // accumulator complete
       }
+#ifdef B200MOE_MEASURE_CYCLES
+      atomicAdd(&g_gemm_cycles[2], static_cast<unsigned long long>(cyc_full));
+      atomicAdd(&g_gemm_cycles[3], static_cast<unsigned long long>(cyc_tmem));
+      atomicAdd(&g_gemm_cycles[4], static_cast<unsigned long long>(clock64() - loop_begin));
+      atomicAdd(&g_gemm_cycles[5], static_cast<unsigned long long>(it));
+#endif
+      (void)cyc_full;
+      (void)cyc_tmem;
     }
     __syncwarp();
   } else {
@@ -723,6 +740,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int quarter = warp & 3;               // TMEM lanes this warp may read: 32*quarter ..
     bool ok = true;
     long long it = 0;
+    long long cyc_drain = 0;
     for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
       const TileCoord c = decode_tile(tile, p.n_tiles, p.num_experts, s_blk_off, p.m_group);
       const int acc = static_cast<int>(it & 1);
@@ -738,16 +756,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // rows padded to 144 bytes.
       uint8_t* stage_out = smem + kStages * kStageBytes +
                            (warp - 2) * ((kIsW13 && p.tma_store) ? 32 * 128 : 32 * kOutStageRowBytes);
+      B200MOE_CYCLES_BEGIN(d0);
       if (kIsW13) {
         drain_w13(p, &tmap_out, taddr, stage_out, c.m_block, c.n_tile, quarter, lane);
       } else {
         drain_w2(p, taddr, stage_out, c.m_block, c.n_tile, quarter, lane);
       }
+      B200MOE_CYCLES_ADD(cyc_drain, d0);
       // Hand the accumulator back to the MMA warp.
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
     }
+#ifdef B200MOE_MEASURE_CYCLES
+    if (warp == 2 && lane == 0) {
+      atomicAdd(&g_gemm_cycles[0], static_cast<unsigned long long>(cyc_drain));
+      atomicAdd(&g_gemm_cycles[1], static_cast<unsigned long long>(it));
+    }
+#endif
+    (void)cyc_drain;
     if (kIsW13 && p.tma_store && lane == 0) tma_store_wait_all();  // before shared memory goes away
   }
 
@@ -824,11 +851,12 @@ constexpr int kDualSmemBytes = kDualStages * kDualStageBytes + kOutStageBytes + 
 // tile.  Measured on B200 at Mixtral shape, interleaved runs: with K = 14336 (second GEMM, 224 K
 // steps) it gains 5-10 % at T = 4096, 8192 and 16384 and loses below about six blocks per expert,
 // where too few tiles are left to deal evenly (T = 2048 with skewed routing: -15 %); with
-// K = 4096 (first GEMM, 64 K steps) it gains 4-5 % at T = 16384 and nothing at T = 4096 and
-// T = 8192, where the one-block kernel also reads less from HBM.  Shorter K loops (the second
-// GEMM of a tensor-parallel shard of eight has 28 K steps) keep the one-block kernel.
+// K = 4096 (first GEMM, 64 K steps) it gains 8-11 % at T = 16384, 0-5 % between T = 5120 and
+// T = 8192 (12 to 16 blocks per expert) and between -2 and +7 % at T = 4096 (8 blocks).  Shorter
+// K loops (the second GEMM of a tensor-parallel shard of eight has 28 K steps) keep the one-block
+// kernel.
 constexpr int kDualLongK = 96, kDualShortK = 48;       // in K steps of 64
-constexpr int kDualMinBlocksLongK = 6, kDualMinBlocksMidK = 24;
+constexpr int kDualMinBlocksLongK = 6, kDualMinBlocksMidK = 12;
 
 // 0: never.
 inline int dual_min_blocks_for(int k_blocks) {
@@ -942,11 +970,20 @@ __host__ __device__ inline int dual_decode(const DualSeq& q, long long tile, Wor
 // The work of CTA `cta` of `grid` in its i-th turn: 0, 1 or 2 items, or -1 when it has no more.
 __host__ __device__ inline int dual_items_at(const DualSeq& q, long long i, int cta, int grid,
                                              WorkItem (&items)[2]) {
-  const long long mine = cta < q.cut ? (q.cut - cta + grid - 1) / grid : 0;
+  // Whole tiles are dealt round by round, and every round starts one CTA further on: the sequence
+  // is periodic (an expert with 37 blocks and slots repeats every 37 tiles: 2 x 18 two-block tiles
+  // and one slot), and a period that divides the grid would hand the same CTAs the dearer tiles
+  // of every round.  Measured at T = 6144 with 37 blocks in the largest expert and 148 CTAs: the
+  // busiest CTA's loop took 21 % longer than the mean without the rotation.
+  const long long rounds = q.cut / grid;
+  const int rest = static_cast<int>(q.cut - rounds * grid);
+  const int last_slot = static_cast<int>((cta + rounds) % grid);
+  const long long mine = rounds + (last_slot < rest ? 1 : 0);
   WorkItem half[2];
   bool joint = false;
   if (i < mine) {
-    const int halves = dual_decode(q, cta + i * grid, half, &joint);
+    const long long tile = i * grid + (i < rounds ? (cta + i) % grid : last_slot);
+    const int halves = dual_decode(q, tile, half, &joint);
     if (joint) {
       items[0] = WorkItem{half[0].expert, half[0].m_block, half[0].n_tile, 2};
       return 1;

@@ -14,7 +14,8 @@ the per-repetition means is printed (under the board's power cap a kernel's time
 ran before it, so only numbers of one run compare).  One JSON line per case and tiling.
 
 ``--cycles`` (needs a library built with ``-DB200MOE_MEASURE_CYCLES`` and passed with ``--lib``)
-forces two-block tiles and prints, per grouped GEMM, what ``b200moe_gemm_measured_cycles`` counted.
+prints, per grouped GEMM and for each of the tilings 1 and 2 named in ``--tilings``, what
+``b200moe_gemm_measured_cycles`` counted.
 """
 from __future__ import annotations
 
@@ -80,13 +81,13 @@ def run_tilings(cases, tilings, steps: int, reps: int, dev) -> None:
                               "gemm_status": lib.b200moe_gemm_device_status(1)}), flush=True)
 
 
-def run_cycles(cases, steps: int, dev) -> None:
+def run_cycles(cases, steps: int, dev, tiling: int = 2) -> None:
     from .layers.moe import fused_moe as fm
     lib = _lib.load()
     out = (ctypes.c_uint64 * 8)()
     if lib.b200moe_gemm_measured_cycles(out, 1) != 1:
         raise SystemExit("--cycles needs a library built with -DB200MOE_MEASURE_CYCLES (pass it with --lib)")
-    _lib.check(lib.b200moe_gemm_set_tiling(2), "set_tiling")
+    _lib.check(lib.b200moe_gemm_set_tiling(tiling), "set_tiling")
     for kind, tokens in cases:
         wl, inp = _base_inputs(kind, tokens, dev)
         x = torch.empty_like(inp["x"])
@@ -118,7 +119,7 @@ def run_cycles(cases, steps: int, dev) -> None:
             fm.enable_kernel_timing(False)
         for key, a in acc.items():
             tiles = max(a[5], 1)
-            print(json.dumps({"routing": kind, "tokens": tokens, "gemm": key,
+            print(json.dumps({"routing": kind, "tokens": tokens, "gemm": key, "tiling": tiling,
                               "cycles_per_tile": a[4] / tiles, "tiles_per_launch": a[5] / steps,
                               "wait_operands_cycles_per_tile": a[2] / tiles,
                               "of_which_first_k_steps": a[6] / tiles, "of_which_last_k_steps": a[7] / tiles,
@@ -144,7 +145,8 @@ def main() -> None:
     dev = torch.device("cuda", 0)
     with torch.inference_mode():
         if args.cycles:
-            run_cycles(cases, min(args.steps, 10), dev)
+            for tiling in [t for t in args.tilings if t in (1, 2)] or [2]:
+                run_cycles(cases, min(args.steps, 10), dev, tiling)
         else:
             run_tilings(cases, args.tilings, args.steps, args.reps, dev)
 

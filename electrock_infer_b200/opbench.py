@@ -7,7 +7,9 @@ At the layer's own token counts the router and alignment move well under a megab
 launch is latency-bound; this sweep runs them at 2^20..2^22 tokens, where their HBM rate is
 meaningful.  Buffers are larger than L2 at these sizes except the router/alignment inputs, so an
 L2-sized buffer is overwritten between timed launches.  Prints one JSON line per op and size with
-the algorithmic bytes, the mean CUDA-event time and GB/s.
+the algorithmic bytes, the mean CUDA-event time and GB/s, and beside them the time a plain device
+copy of the same number of bytes takes under the same timing (a launch of a few tens of megabytes
+does not reach the large-copy rate whatever it does).
 """
 from __future__ import annotations
 
@@ -51,9 +53,25 @@ def main() -> None:
     flush = torch.zeros(64 << 20, dtype=torch.int32, device=dev)  # 256 MiB > L2
     g = torch.Generator(device=dev).manual_seed(0)
 
+    copy_ms = {}
+
+    def same_bytes_copy_ms(nbytes):
+        """A plain device copy that moves the same bytes (half read, half written): what a launch of
+        this size can reach at all, ramp-up and tail included."""
+        half = max(nbytes // 2 // 16 * 16, 16)
+        if half not in copy_ms:
+            src = torch.empty(half, dtype=torch.uint8, device=dev)
+            dst = torch.empty_like(src)
+            copy_ms[half] = time_op(lambda: dst.copy_(src), args.iters, flush)
+            del src, dst
+        return copy_ms[half]
+
     def report(op, tokens, nbytes, ms, **kw):
+        cms = same_bytes_copy_ms(nbytes)
         print(json.dumps({"op": op, "tokens": tokens, "algorithmic_bytes": nbytes,
-                          "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), **kw}), flush=True)
+                          "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1),
+                          "same_bytes_copy_ms": round(cms, 5),
+                          "time_vs_copy": round(ms / cms, 2), **kw}), flush=True)
 
     for T in ([] if args.only_kv else args.tokens):
         logits = torch.randn(T, 8, generator=g, device=dev)
