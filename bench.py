@@ -51,13 +51,15 @@ from electrock_infer_b200.synthetic import WORKLOADS, MoEWorkload, make_inputs  
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 # DRAM traffic (ncu: dram__bytes_read.sum + dram__bytes_write.sum) over algorithmic bytes, per
-# grouped-GEMM kernel, from one captured launch of each at T=4096 with the tilings the benchmark
-# workload runs (first GEMM: one M block per tile, 2.203 / 2.200 GB; second GEMM: two M blocks per
-# tile, 1.997 / 1.256 GB: its weights are streamed once per L2-sized group of A rows by design).
-# Traffic is weights + rows x (K + N) x 2 bytes, so a full-size launch is scaled by the same ratio.
-NCU_TRAFFIC_RATIO = {"grouped_gemm_w13_swiglu": 1.001, "grouped_gemm_w2_scale": 1.59}
+# grouped-GEMM kernel, from one captured launch of each on the benchmark workload itself (T=8192,
+# skewed routing, both GEMMs with two M blocks per tile): first GEMM 3.263 GB against 2.483 GB,
+# second GEMM 3.232 GB against 1.544 GB.  The second GEMM streams an expert's weights once per
+# L2-sized group of A rows by design (17 passes over 117 MB for this routing); the first GEMM
+# re-reads weight tiles where CTAs working on one tile drift apart and for the second group of
+# the 50-block expert.  Other token counts are scaled by the same ratio.
+NCU_TRAFFIC_RATIO = {"grouped_gemm_w13_swiglu": 1.314, "grouped_gemm_w2_scale": 2.094}
 NCU_TRAFFIC_NOTE = ("algorithmic bytes x the ncu DRAM read+write / algorithmic ratio of a captured "
-                    "launch of the same kernel at a smaller T")
+                    "launch of the same kernel on mixtral_prefill_t8192_skew")
 PARITY_TOKENS = 64
 PARITY_MAX_ABS, PARITY_REL_FRO = 3e-2, 1e-2
 # Device buffers of the end-to-end pipeline: step i+3's upload waits for step i's download (the
