@@ -446,7 +446,7 @@ int b200moe_gemm_measured_cycles(uint64_t* out8, int reset);
  * tests: 0 (default) chooses by batch size, 1 forces one 128-row M block per tile (128 x 256
  * accumulator, double-buffered in tensor memory), 2 forces two M blocks of one expert per tile
  * (they share every weight stage; chosen by default, on the device from the real block counts:
- * from about six M blocks per expert on when K is at least 6144, from about twenty-four when K is
+ * from about six M blocks per expert on when K is at least 6144, from about twelve when K is
  * at least 3072, never for shorter K).
  * All tilings produce the same bits.  The reference's counterpart is the tile configuration table
  * of layers/moe/fused_moe.py:327-339.  Returns 0 or B200MOE_ERR_SHAPE.
