@@ -39,7 +39,10 @@ def _worker_full_size(rank, port, mode, result_dir):
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+    # Rendezvous through a file in the test's own directory: a TCP port found free by the parent can
+    # be taken again before the workers bind it.
+    dist.init_process_group("nccl", init_method=f"file://{result_dir}/rendezvous", rank=rank,
+                            world_size=WORLD, device_id=dev)
     wl = WORKLOADS["mixtral_parallel_t16384"]
     T, I = wl.num_tokens, wl.inter
     full = make_inputs(wl, device=dev, device_rng=True)
@@ -116,7 +119,10 @@ def _worker(rank, port, mode, result_dir):
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+    # Rendezvous through a file in the test's own directory: a TCP port found free by the parent can
+    # be taken again before the workers bind it.
+    dist.init_process_group("nccl", init_method=f"file://{result_dir}/rendezvous", rank=rank,
+                            world_size=WORLD, device_id=dev)
     tokens = 6 if mode == "ep_peer_tiny" else 600
     wl = MoEWorkload("par", tokens, 512, 1024, seed=23, logit_bias=(2, 1, 0.5, 0, 0, -0.5, -1, -2))
     full = make_inputs(wl)
