@@ -80,6 +80,7 @@ SIGNATURES = {
     "b200moe_gemm_measured_cycles": (c_int, [c_void_p, c_int]),
     "b200moe_gemm_set_act_stores": (c_int, [c_int]),
     "b200moe_gemm_set_tiling": (c_int, [c_int]),
+    "b200moe_gemm_two_block_choice": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_int]),
     "b200moe_gemm_two_block_schedule": (c_int64, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                   c_void_p, c_int64]),
 }

@@ -327,19 +327,56 @@ struct GemmParams {
   int top_k;                     // kW13Gather: A row of slot s is sorted[s] / top_k
   int num_src_rows;              // kW13Gather: rows of the token tensor
   int tma_store;                 // kW13: rows leave the SM as bulk tensor stores (half_n % 64 == 0)
-  int dual_min_blocks;           // > 0: the one-block and the two-block kernel are both launched and
-                                 // decide on the device which of them runs (two_block_tiles_win)
+  int dual_pair_cost;            // > 0: the one-block and the two-block kernel are both launched and
+                                 // decide on the device which of them runs (two_block_tiles_win);
+                                 // time of a two-block tile in percent of a one-block tile's
+  int dual_single_cost;          // ... and of a one-block item inside the two-block kernel
+  int dual_ctas;                 // CTAs the work is dealt to (the SM count)
+  int dual_slots;                // odd blocks are dealt as slots (first GEMM)
 };
 
 // The choice between one and two M blocks per tile, made on the device from the real block counts
 // (the host only knows an upper bound of the rows, and under expert parallelism that bound is the
 // whole batch while a rank receives a fraction of it).  Both kernels of a launch pair evaluate
 // it on the same counts; exactly one of them does the work, the other returns after its prologue.
-__device__ __forceinline__ bool two_block_tiles_win(const int* blk_off, int num_experts,
-                                                    int min_blocks_per_expert) {
-  int busy = 0;
-  for (int e = 0; e < num_experts; ++e) busy += blk_off[e + 1] > blk_off[e] ? 1 : 0;
-  return busy > 0 && blk_off[num_experts] >= min_blocks_per_expert * busy;
+//
+// It compares estimated finishing times, in percent of a one-block tile's time.  One-block tiles:
+// whole rounds of `ctas` tiles.  Two-block tiles, measured in interleaved runs at Mixtral shape:
+// a tile of two blocks takes 1.82-1.84 one-block tiles (it issues MMAs 93-98 % of the time against
+// 84 %, but the board sits at its power cap either way), an odd block's one-block item inside the
+// two-block kernel 1.16 (K = 14336) to 1.4 (K = 4096, where the exposed drain weighs more).
+// With slots (first GEMM) every unit costs about two and the rounds are long, so the estimate is
+// the mean share plus half a unit; without (second GEMM: 16 N tiles, a handful of rounds) units are
+// dealt round-robin whatever they cost (whole rounds at the mean cost of a unit), and a last round
+// at most half full is dealt in halves.
+// Two-block tiles must win by 3 %.  This reproduces what was measured: second GEMM, skewed
+// routing: one-block tiles at T = 2048, 2560 and 3072 (-15, -3 and -7 % for two-block tiles),
+// two-block tiles at T = 4096 and 8192 (+10 and +8 %); first GEMM: one-block at T = 2048 and 3072,
+// two-block from T = 4096 on (0 to +8 %).
+__host__ __device__ inline bool two_block_tiles_win(const int* blk_off, int num_experts, int n_tiles,
+                                                    int ctas, int pair_cost, int single_cost,
+                                                    bool slots) {
+  long long blocks = 0, pairs = 0, singles = 0;
+  for (int e = 0; e < num_experts; ++e) {
+    const int cnt = blk_off[e + 1] - blk_off[e];
+    blocks += cnt;
+    pairs += cnt >> 1;
+    singles += cnt & 1;
+  }
+  if (pairs == 0 || ctas <= 0) return false;
+  const long long one_block = (blocks * n_tiles + ctas - 1) / ctas * 100;
+  long long two_block;
+  if (slots) {
+    const long long work = pairs * n_tiles * pair_cost + singles * n_tiles * single_cost;
+    two_block = (work + ctas - 1) / ctas + pair_cost / 2;
+  } else {
+    const long long items = (pairs + singles) * n_tiles;
+    const long long rest = items % ctas;
+    const long long mean_cost = (pairs * pair_cost + singles * single_cost) / (pairs + singles);
+    two_block = items / ctas * mean_cost +
+                (rest == 0 ? 0 : (2 * rest > ctas ? pair_cost : single_cost));
+  }
+  return two_block * 103 < one_block * 100;
 }
 
 
@@ -613,7 +650,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   long long total_tiles = static_cast<long long>(s_blk_off[p.num_experts]) * p.n_tiles;
-  if (p.dual_min_blocks > 0 && two_block_tiles_win(s_blk_off, p.num_experts, p.dual_min_blocks))
+  if (p.dual_pair_cost > 0 &&
+      two_block_tiles_win(s_blk_off, p.num_experts, p.n_tiles, p.dual_ctas, p.dual_pair_cost,
+                          p.dual_single_cost, p.dual_slots != 0))
     total_tiles = 0;  // the two-block kernel launched beside this one does the work
   volatile int* abort_flag = &s_abort;
 
@@ -850,23 +889,21 @@ __device__ __forceinline__ uint64_t make_dual_desc(uint32_t smem_addr) {
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 constexpr int kDualSmemBytes = kDualStages * kDualStageBytes + kOutStageBytes + kSmemAlignSlack;
-// When the two-block kernel is chosen: from an average number of M blocks per expert that has any
-// (counted on the device, see two_block_tiles_win) which depends on the length of the K loop,
-// because the part of the drain that no longer overlaps the next tile's MMAs is paid once per
-// tile.  Measured on B200 at Mixtral shape, interleaved runs: with K = 14336 (second GEMM, 224 K
-// steps) it gains 5-10 % at T = 4096, 8192 and 16384 and loses below about six blocks per expert,
-// where too few tiles are left to deal evenly (T = 2048 with skewed routing: -15 %); with
-// K = 4096 (first GEMM, 64 K steps) it gains 8-11 % at T = 16384, 0-5 % between T = 5120 and
-// T = 8192 (12 to 16 blocks per expert) and between -2 and +7 % at T = 4096 (8 blocks).  Shorter
-// K loops (the second GEMM of a tensor-parallel shard of eight has 28 K steps) keep the one-block
-// kernel.
-constexpr int kDualLongK = 96, kDualShortK = 48;       // in K steps of 64
-constexpr int kDualMinBlocksLongK = 6, kDualMinBlocksMidK = 12;
-
-// 0: never.
-inline int dual_min_blocks_for(int k_blocks) {
-  return k_blocks >= kDualLongK ? kDualMinBlocksLongK : (k_blocks >= kDualShortK ? kDualMinBlocksMidK : 0);
+// Cost constants of two_block_tiles_win by length of the K loop (in K steps of 64): the part of
+// the drain that no longer overlaps the next tile's MMAs is paid once per tile, so short K loops
+// (the second GEMM of a tensor-parallel shard of eight has 28 K steps) keep the one-block kernel.
+constexpr int kDualLongK = 96, kDualShortK = 48;
+struct DualCost {
+  int pair, single;  // percent of a one-block tile's time; pair == 0: never two-block tiles
+};
+inline DualCost dual_cost_for(int k_blocks) {
+  if (k_blocks >= kDualLongK) return DualCost{182, 116};
+  if (k_blocks >= kDualShortK) return DualCost{184, 140};
+  return DualCost{0, 0};
 }
+// Both kernels are launched (and decide on the device) from this many M blocks per expert in the
+// upper bound the host knows; below it two-block tiles never win.
+constexpr int kDualHostGateBlocks = 6;
 
 // One piece of work of the two-block kernel: m_count = 2 is two M blocks (m_block, m_block + 1) of
 // one expert against one N tile; m_count = 1 is a single block.
@@ -1085,7 +1122,9 @@ grouped_gemm_dual_kernel(const __grid_constant__ CUtensorMap tmap_a,    // box o
   seq.unit_group = p.m_group > 0 ? (p.m_group + 1) / 2 : 0;
   seq.slots = kMode != kW2;
   seq.total = s_tile_off[p.num_experts];
-  if (p.dual_min_blocks > 0 && !two_block_tiles_win(s_blk_off, p.num_experts, p.dual_min_blocks))
+  if (p.dual_pair_cost > 0 &&
+      !two_block_tiles_win(s_blk_off, p.num_experts, p.n_tiles, p.dual_ctas, p.dual_pair_cost,
+                           p.dual_single_cost, p.dual_slots != 0))
     seq.total = 0;  // the one-block kernel launched beside this one does the work
   seq.cut = dual_cut(seq.total, grid);
 
@@ -1717,14 +1756,15 @@ enum TileChoice { kOneBlock, kTwoBlock, kDecideOnDevice };
 
 // kOneBlock when even the upper bound of the rows is too small for two-block tiles to pay (only
 // the one-block kernel is launched); kDecideOnDevice otherwise: both kernels are launched and the
-// real block counts decide (GemmParams::dual_min_blocks).
-TileChoice choose_tiles(int64_t capacity, int num_experts, int min_blocks_per_expert) {
+// real block counts decide (two_block_tiles_win).
+TileChoice choose_tiles(int64_t capacity, int num_experts, const DualCost& cost) {
   const int mode = g_tiling.load(std::memory_order_relaxed);
   if (capacity < 2 * kBlockM || mode == 1) return kOneBlock;
   if (mode == 2) return kTwoBlock;
-  if (min_blocks_per_expert <= 0) return kOneBlock;
+  if (cost.pair <= 0) return kOneBlock;
   const int64_t pairs = capacity - static_cast<int64_t>(num_experts) * (kBlockM - 1);
-  return pairs >= static_cast<int64_t>(kBlockM) * min_blocks_per_expert ? kDecideOnDevice : kOneBlock;
+  return pairs >= static_cast<int64_t>(kBlockM) * kDualHostGateBlocks * num_experts ? kDecideOnDevice
+                                                                                    : kOneBlock;
 }
 
 // Tensor maps of the two-block kernel (its own K step and swizzle): A rows in boxes of one and of
@@ -1741,11 +1781,14 @@ int make_dual_maps(DualMaps* m, const void* a, long long a_rows, long long k, co
 }
 
 template <int kMode>
-int launch_chosen(TileChoice choice, int min_blocks, const CUtensorMap& ta, const CUtensorMap& tb,
+int launch_chosen(TileChoice choice, const DualCost& cost, const CUtensorMap& ta, const CUtensorMap& tb,
                   const CUtensorMap& tout, const DualMaps& dm, GemmParams p, cudaStream_t st) {
   if (choice == kOneBlock) return launch<kMode>(ta, tb, tout, p, st);
   if (choice == kTwoBlock) return launch_dual<kMode>(dm.a, dm.a2, dm.b, tout, p, st);
-  p.dual_min_blocks = min_blocks;
+  p.dual_pair_cost = cost.pair;
+  p.dual_single_cost = cost.single;
+  p.dual_ctas = sm_count();
+  p.dual_slots = kMode != kW2 ? 1 : 0;
   if (int rc = launch<kMode>(ta, tb, tout, p, st)) return rc;
   return launch_dual<kMode>(dm.a, dm.a2, dm.b, tout, p, st);
 }
@@ -1841,8 +1884,8 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   if (!aligned_to(a_sorted, 16) || !aligned_to(w13, 16) || !aligned_to(act, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
   // The two-CTA kernel has a fixed 128 + 128 column tile; the one-CTA kernels pick their width.
-  const int dual_min_blocks = dual_min_blocks_for(static_cast<int>(hidden / kBlockK));
-  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_min_blocks)
+  const DualCost dual_cost = dual_cost_for(static_cast<int>(hidden / kBlockK));
+  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_cost)
                                               : kOneBlock;
   const bool two_block = tiles != kOneBlock;
   const int half_n = block_m == kPairBlockM ? kBlockN / 2
@@ -1877,7 +1920,7 @@ extern "C" int b200moe_grouped_gemm_w13_swiglu(const void* a_sorted, const void*
   p.tma_store = (half_n % 64 == 0 && g_tma_act_stores.load(std::memory_order_relaxed)) ? 1 : 0;
   if (p.tma_store)
     if (int rc = make_tmap(&tout, act, sorted_capacity, inter, 32, name)) return rc;
-  return launch_chosen<kW13>(tiles, dual_min_blocks, ta, tb, tout, dm, p,
+  return launch_chosen<kW13>(tiles, dual_cost, ta, tb, tout, dm, p,
                              static_cast<cudaStream_t>(stream));
 }
 
@@ -1952,8 +1995,8 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16) || !aligned_to(out, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  const int dual_min_blocks = dual_min_blocks_for(static_cast<int>(inter / kBlockK));
-  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_min_blocks)
+  const DualCost dual_cost = dual_cost_for(static_cast<int>(inter / kBlockK));
+  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_cost)
                                               : kOneBlock;
   const bool two_block = tiles != kOneBlock;
   CUtensorMap ta, tb;
@@ -1984,7 +2027,7 @@ extern "C" int b200moe_grouped_gemm_w2_scale(const void* act, const void* w2, vo
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, ta, dm, p, static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, dual_cost, ta, tb, ta, dm, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_w2_scale_peer(
@@ -2009,8 +2052,8 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
     return fail(B200MOE_ERR_NULL, "%s: null pointer", name);
   if (!aligned_to(act, 16) || !aligned_to(w2, 16))
     return fail(B200MOE_ERR_ALIGN, "%s: operands must be 16-byte aligned", name);
-  const int dual_min_blocks = dual_min_blocks_for(static_cast<int>(inter / kBlockK));
-  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_min_blocks)
+  const DualCost dual_cost = dual_cost_for(static_cast<int>(inter / kBlockK));
+  const TileChoice tiles = block_m == kBlockM ? choose_tiles(sorted_capacity, num_experts, dual_cost)
                                               : kOneBlock;
   const bool two_block = tiles != kOneBlock;
   CUtensorMap ta, tb;
@@ -2042,7 +2085,26 @@ extern "C" int b200moe_grouped_gemm_w2_scale_peer(
   set_width(&p, kBlockN);
   p.m_group = m_group_for(inter * 2);
   if (block_m == kPairBlockM) return launch_pair<kW2>(ta, tb, p, static_cast<cudaStream_t>(stream));
-  return launch_chosen<kW2>(tiles, dual_min_blocks, ta, tb, ta, dm, p, static_cast<cudaStream_t>(stream));
+  return launch_chosen<kW2>(tiles, dual_cost, ta, tb, ta, dm, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_gemm_two_block_choice(const int32_t* blocks_per_expert, int num_experts,
+                                             int n_tiles, int64_t k, int slots, int ctas) {
+  using namespace b200moe;
+  if (!blocks_per_expert || num_experts < 1 || num_experts > kMaxExperts || n_tiles < 1 || k < 1 ||
+      ctas < 1)
+    return fail(B200MOE_ERR_SHAPE, "gemm_two_block_choice: bad arguments");
+  int blk_off[kMaxExperts + 1];
+  blk_off[0] = 0;
+  for (int e = 0; e < num_experts; ++e) {
+    if (blocks_per_expert[e] < 0)
+      return fail(B200MOE_ERR_SHAPE, "gemm_two_block_choice: negative block count");
+    blk_off[e + 1] = blk_off[e] + blocks_per_expert[e];
+  }
+  const DualCost cost = dual_cost_for(static_cast<int>(k / kBlockK));
+  if (cost.pair <= 0) return 0;
+  return two_block_tiles_win(blk_off, num_experts, n_tiles, ctas, cost.pair, cost.single, slots != 0)
+             ? 1 : 0;
 }
 
 extern "C" int64_t b200moe_gemm_two_block_schedule(const int32_t* blocks_per_expert, int num_experts,

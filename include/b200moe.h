@@ -445,9 +445,9 @@ int b200moe_gemm_measured_cycles(uint64_t* out8, int reset);
  * Tiling of the one-CTA grouped GEMMs (block_m = 128), a process-wide setting for benchmarks and
  * tests: 0 (default) chooses by batch size, 1 forces one 128-row M block per tile (128 x 256
  * accumulator, double-buffered in tensor memory), 2 forces two M blocks of one expert per tile
- * (they share every weight stage; chosen by default, on the device from the real block counts:
- * from about six M blocks per expert on when K is at least 6144, from about twelve when K is
- * at least 3072, never for shorter K).
+ * (they share every weight stage; chosen by default, on the device from the real block counts,
+ * where its estimated finishing time is 3 % below that of one-block tiles, see
+ * b200moe_gemm_two_block_choice; never when K is below 3072).
  * All tilings produce the same bits.  The reference's counterpart is the tile configuration table
  * of layers/moe/fused_moe.py:327-339.  Returns 0 or B200MOE_ERR_SHAPE.
  */
@@ -460,6 +460,19 @@ int b200moe_gemm_set_tiling(int mode);
  * bits either way.  No counterpart in the reference.
  */
 int b200moe_gemm_set_act_stores(int bulk);
+
+/*
+ * Host-side view of the choice between one and two M blocks per tile that the grouped GEMMs make
+ * on the device under b200moe_gemm_set_tiling(0): 1 when two-block tiles would run for experts
+ * holding `blocks_per_expert[e]` M blocks of 128 rows, an output of `n_tiles` N tiles, a reduction
+ * length `k`, `ctas` CTAs (the SM count) and the odd blocks dealt as slots (`slots` non-zero: the
+ * first GEMM) or not; 0 when one-block tiles would.  The rule compares estimated finishing times
+ * (see two_block_tiles_win in csrc/grouped_gemm.cu).  Runs on the host; no device is touched.
+ * Returns 0, 1 or a negative B200MOE_ERR_*.  No counterpart in the reference beyond its tile
+ * configuration table (layers/moe/fused_moe.py:327-339).
+ */
+int b200moe_gemm_two_block_choice(const int32_t* blocks_per_expert, int num_experts, int n_tiles,
+                                  int64_t k, int slots, int ctas);
 
 /*
  * Host-side view of the work list of the two-block tiling, for tests and tuning: the items that

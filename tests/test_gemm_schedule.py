@@ -80,3 +80,42 @@ def test_bad_arguments_are_refused():
     assert lib.b200moe_gemm_two_block_schedule(b.ctypes.data, 2, 4, 0, 1, 148, 0, None, 0) < 0
     assert lib.b200moe_gemm_two_block_schedule(None, 2, 4, 0, 1, 148, 0, None, 0) < 0
     assert lib.b200moe_gemm_two_block_schedule(b.ctypes.data, 2, 4, 0, 0, 148, 148, None, 0) < 0
+
+
+def choice(blocks, n_tiles, k, slots, ctas=148):
+    b = np.asarray(blocks, dtype=np.int32)
+    return _lib.load().b200moe_gemm_two_block_choice(b.ctypes.data, len(blocks), n_tiles, k, slots, ctas)
+
+
+# Block counts per expert of the skewed benchmark routing (mixtral_prefill_t8192_skew cut to T
+# tokens) and of near-uniform routing, with what interleaved runs on a B200 measured as the faster
+# tiling of each grouped GEMM (1 = two M blocks per tile).  Sizes where the two tilings measured
+# within run-to-run noise are left out.
+MEASURED = [
+    ("skew T=2048", [13, 8, 5, 3, 3, 2, 1, 1], 0, 0),
+    ("skew T=3072", [19, 11, 8, 5, 5, 3, 2, 1], 0, 0),
+    ("skew T=4096", [25, 15, 10, 6, 6, 3, 2, 1], None, 1),
+    ("skew T=6144", [37, 22, 15, 8, 9, 5, 3, 1], None, 1),
+    ("skew T=8192", [50, 29, 20, 12, 11, 6, 3, 1], 1, 1),
+    ("uniform T=2048", [5, 4, 4, 5, 4, 4, 5, 4], None, 0),
+    ("uniform T=3072", [7, 6, 7, 6, 6, 7, 6, 7], None, 0),
+    ("uniform T=16384", [33] * 8, 1, 1),
+]
+
+
+@pytest.mark.parametrize("name,blocks,first,second", MEASURED, ids=[m[0] for m in MEASURED])
+def test_tiling_choice_follows_the_measurements(name, blocks, first, second):
+    """The device-side rule (estimated finishing times of the two tilings), evaluated on the host
+    for Mixtral-8x7B's two GEMMs: N tiles 14336/128 and 4096/256, K 4096 and 14336."""
+    if first is not None:
+        assert choice(blocks, 112, 4096, 1) == first
+    if second is not None:
+        assert choice(blocks, 16, 14336, 0) == second
+
+
+def test_tiling_choice_edge_cases():
+    assert choice([1, 1, 1, 1, 1, 1, 1, 1], 112, 4096, 1) == 0      # no pair of blocks anywhere
+    assert choice([0, 0, 0, 0, 0, 0, 0, 0], 16, 14336, 0) == 0
+    assert choice([33] * 8, 16, 1792, 0) == 0                        # short K: never two-block tiles
+    assert choice([33], 16, 14336, 0) == 1                           # one expert per rank (eight GPUs)
+    assert choice([33], 16, 14336, 0, ctas=0) < 0 and choice([-1], 16, 14336, 0) < 0
