@@ -40,7 +40,7 @@ def time_op(fn, iters: int, flush: torch.Tensor) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, nargs="+", default=[1 << 20, 1 << 21, 1 << 22])
-    ap.add_argument("--combine-tokens", type=int, nargs="+", default=[8192, 16384, 65536])
+    ap.add_argument("--combine-tokens", type=int, nargs="+", default=[2048, 8192, 16384, 65536])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--skip-kv", action="store_true", help="leave out the paged KV-cache ops")
