@@ -59,16 +59,20 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _init(rank, port):
+def _init(rank, port, result_dir):
+    # MASTER_* stay set for code that reads them; the rendezvous itself goes through a file in the
+    # test's own directory, because a TCP port found free by the parent can be taken again before
+    # the workers bind it.
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    dist.init_process_group("gloo", init_method=f"file://{result_dir}/rendezvous", rank=rank,
+                            world_size=WORLD)
 
 
 def _ep_worker(rank, port, skew, result_dir):
     from electrock_infer_b200.parallel import ExpertParallelMoE
     from oracle import moe_oracle
-    _init(rank, port)
+    _init(rank, port, result_dir)
     bias = (3, 2, 1, 0, 0, -1, -2, -9) if skew else None
     wl = MoEWorkload("ep", 70, 32, 64, dtype=torch.float32, seed=17, logit_bias=bias)
     full = make_inputs(wl)
@@ -102,7 +106,7 @@ def test_expert_parallel_exchange_on_gloo(tmp_path, skew):
 def _tp_worker(rank, port, result_dir):
     from electrock_infer_b200.layers.moe import FusedMoE, mixtral_moe
     from oracle import moe_oracle
-    _init(rank, port)
+    _init(rank, port, result_dir)
     wl = MoEWorkload("tp", 33, 32, 64, dtype=torch.float32, seed=19)
     full = make_inputs(wl)
 
@@ -159,7 +163,7 @@ def _decision_worker(rank, port, result_dir):
     call, what ``peer_capacity`` answers; with the oracle stand-in every call then runs the NCCL
     exchange to the end, which would hang if the ranks disagreed."""
     from electrock_infer_b200.parallel import ExpertParallelMoE, TensorParallelReduce
-    _init(rank, port)
+    _init(rank, port, result_dir)
     wl = MoEWorkload("ep", 100, 32, 64, dtype=torch.float32, seed=5)
     full = make_inputs(wl)
     counts = [(50, 50), (50, 45), (50, 50), (10, 0), (0, 30), (50, 50)]  # (rank 0, rank 1) per call
